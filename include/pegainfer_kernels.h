@@ -516,6 +516,46 @@ int pk_moe_up_act(const void* xa, const void* w_up, const int* ids, void* hid, i
 int pk_moe_grouped_act(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
                        const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act, pk_stream st);
 
+/* =============== sandwich blocks with grouped RMS norm, attention options, windowed latent attention ===============
+ * gnorm(v, w)[i] = v[i] / sqrt(mean over i's group of v^2 + eps) * w[i]; a row of `width` entries is `groups` equal consecutive parts.
+ * A sandwich block norms the input AND the result of every sublayer: x += mult * gnorm(gated f(gnorm(x, w_pre)), w_post). */
+/* x[t] = gnorm(embed[ids[t]], w_embed) (fp32 residual);  h[t] = gnorm(x[t], w_next) in the element type when w_next != NULL */
+int pk_res32_embed_gnorm(const void* embed, const int* token_ids, const void* w_embed, float* x, const void* w_next, void* h, int width, int groups,
+                         float eps, int tokens, int f32, pk_stream st);
+/* x[t] += mult * gnorm((y[t] + bias) * logistic(gate[t * gate_ld + :] + gate_bias), w_post);  h[t] = gnorm(x[t], w_next) when w_next != NULL.
+ * y: element type, or float when y_is_f32.  bias, gate, gate_bias may be NULL (no bias / no gate).  -2: row too wide for shared memory. */
+int pk_res32_gated_gnorm_add(const void* y, int y_is_f32, const void* bias, const void* gate, long gate_ld, const void* gate_bias, const void* w_post,
+                             float mult, float* x, const void* w_next, void* h, int width, int groups, float eps, int tokens, int f32, pk_stream st);
+/* out[r] = gnorm(x[rows[r]], w) in the element type (rows == NULL: every row) */
+int pk_res32_gnorm_rows(const float* x, const int* rows, const void* w, void* out, int width, int groups, float eps, int n_rows, int f32, pk_stream st);
+/* pk_gqa_rope_append with an unweighted RMS norm of every value head before it is cached (value_norm_eps > 0; 0 = as pk_gqa_rope_append).
+ * dims == 0: nothing rotates and freq may be NULL. */
+int pk_gqa_rope_append_ex(const void* qkv, int ld, const void* bias, const int* positions, const int* req, const int* page_off, const int* pages,
+                          void* q_out, void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim, int vdim, int dims,
+                          int interleaved, const float* freq, float mag, float value_norm_eps, int tokens, int f32, pk_stream st);
+/* Options of pk_gqa_attention_ex; a zero / NULL field switches its option off. */
+typedef struct pk_attn_extra {
+  int window;        /* query at position p sees keys p - window + 1 .. p (combined with `chunk`: the later of the two starts) */
+  float softcap;     /* scaled score <- softcap * tanh(score / softcap) */
+  float slope_log2;  /* head h subtracts 2^(-slope_log2 (h + 1) / heads) * (p - j) from the (capped) score of key j */
+  const void* gate;  /* element type, rows of stride gate_ld: out[t, h, d] *= logistic(gate[t * gate_ld + h * vdim + d]) */
+  long gate_ld;
+} pk_attn_extra;
+/* pk_gqa_attention with those options (extra == NULL: none).  A sink of score zero ("one added to the denominator") is a sink vector of zeros. */
+int pk_gqa_attention_ex(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                        const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim, int vdim,
+                        float scale, int chunk, const pk_attn_extra* extra, int f32, pk_stream st);
+/* pk_rope_slice / pk_latent_kv_append with a choice of pairing: interleaved 1 rotates (2i, 2i + 1), 0 rotates (i, i + dims/2) */
+int pk_rope_slice_ex(const void* in, void* out, const int* positions, const float* freq, float mag, int tokens, int heads, int in_stride, int in_off,
+                     int out_stride, int out_off, int width, int dims, int interleaved, int f32, pk_stream st);
+int pk_latent_kv_append_ex(const void* dkv, const void* norm_w, const int* positions, const int* req, const int* page_off, const int* pages,
+                           void* cache, long page_stride, int page_size, int rank, int rot, int dims, int interleaved, const float* freq, float mag,
+                           float eps, int tokens, int f32, pk_stream st);
+/* pk_latent_attention with a sliding window (window > 0: keys p - window + 1 .. p) and an optional sink (NULL: ordinary softmax) */
+int pk_latent_attention_ex(const void* qa, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                           const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
+                           int window, int max_kv_len, int f32, pk_stream st);
+
 #ifdef __cplusplus
 }
 #endif

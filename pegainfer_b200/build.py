@@ -47,6 +47,8 @@ PARTS_OF = {
                 ("qwen3_host.cpp", "layered_host.cpp")),
     "Risolorn": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "gqa_attention.cu", "recurrent_mixers.cu", "moe.cu", "moe_grouped.cu"),
                  ("qwen3_host.cpp", "layered_host.cpp")),
+    "Nagosun": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "gqa_attention.cu", "latent_attention.cu", "latent_attention_mma.cu"),
+                ("qwen3_host.cpp", "layered_host.cpp")),
 }
 MANIFEST = os.path.join(OBJ, "linked.txt")
 

@@ -3,6 +3,9 @@
 // table (pairs interleaved (2i, 2i+1) or split in halves (i, i + dims/2); plain, YaRN or any other schedule is the
 // host's table), a chunk-local causal mask (query at position p sees keys floor(p / chunk) * chunk .. p; chunk 0 = plain
 // causal) and a learned per-head sink that adds exp(sink) to the softmax denominator without a value.
+// Further options (pk_attn_extra): a sliding window (keys p - window + 1 .. p), a soft cap on the scaled score
+// (cap * tanh(score / cap)), a linear distance bias (head h subtracts 2^(-slope_log2 (h + 1) / heads) * (p - j)), an
+// element-wise logistic gate on the output, and -- in the append -- an unweighted RMS norm of every cached value head.
 //
 // Cache: token at position p of a request lives in page pages[page_off[req] + p / page_size], slot p % page_size, at
 //   cache + page * page_stride + slot * (G * dim + G * vdim):  [K of G heads | V of G heads].
@@ -22,14 +25,28 @@ template <typename E>
 __global__ void gqa_rope_append_kernel(const E* __restrict__ qkv, int ld, const E* __restrict__ bias, const int* __restrict__ pos,
                                        const int* __restrict__ req, const int* __restrict__ page_off, const int* __restrict__ pages,
                                        E* __restrict__ q_out, E* __restrict__ cache, long page_stride, int page_size, int H, int G, int dim, int vdim,
-                                       int dims, int interleaved, const float* __restrict__ freq, float mag) {
+                                       int dims, int interleaved, const float* __restrict__ freq, float mag, float v_eps) {
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, p = pos[t];
   const E* row = qkv + (size_t)t * ld;
   const int nq = H * dim, nk = G * dim, nv = G * vdim, half = dims >> 1;
   E* slot = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (nk + nv);
-  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < nq + nk + nv; e += gridDim.y * blockDim.x) {
+  if (v_eps > 0.f) {  // cached values are unit-RMS per head: one warp per value head
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = blockIdx.y * nw + (threadIdx.x >> 5); g < G; g += gridDim.y * nw) {
+      const int e0 = nq + nk + g * vdim;
+      float ss = 0.f;
+      for (int d = lane; d < vdim; d += 32) {
+        const float v = to_f(row[e0 + d]) + (bias ? to_f(bias[e0 + d]) : 0.f);
+        ss = fmaf(v, v, ss);
+      }
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)vdim + v_eps);
+      for (int d = lane; d < vdim; d += 32) slot[e0 - nq + d] = from_f<E>((to_f(row[e0 + d]) + (bias ? to_f(bias[e0 + d]) : 0.f)) * inv);
+    }
+  }
+  const int n_el = v_eps > 0.f ? nq + nk : nq + nk + nv;
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < n_el; e += gridDim.y * blockDim.x) {
     float v = to_f(row[e]) + (bias ? to_f(bias[e]) : 0.f);
     if (e < nq + nk) {
       const int d = (e < nq ? e : e - nq) % dim;
@@ -56,6 +73,25 @@ __global__ void gqa_rope_append_kernel(const E* __restrict__ qkv, int ld, const 
   }
 }
 
+// the options of pk_attn_extra as the kernels take them (all off when zero / null)
+struct AttnExtra {
+  int window;
+  float softcap, slope_log2;
+  const void* gate;
+  long gate_ld;
+};
+__device__ __forceinline__ int first_visible(int p, int chunk, int window) {
+  int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  if (window > 0) lo = max(lo, p - window + 1);
+  return lo;
+}
+__device__ __forceinline__ float head_slope(float slope_log2, int h, int H) { return slope_log2 > 0.f ? exp2f(-slope_log2 * (float)(h + 1) / (float)H) : 0.f; }
+// scaled score -> soft cap -> minus the distance bias
+__device__ __forceinline__ float shape_score(float s, float softcap, float slope, int distance) {
+  if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+  return s - slope * (float)distance;
+}
+
 constexpr int kGqaWarps = 4;
 constexpr int kGqaMaxPerLane = 8;  // features per lane: dim, vdim <= 256
 
@@ -64,13 +100,14 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
                                                                       const int* __restrict__ pos, const int* __restrict__ req,
                                                                       const int* __restrict__ page_off, const int* __restrict__ pages,
                                                                       E* __restrict__ out, long page_stride, int page_size, int H, int G, int dim,
-                                                                      int vdim, float scale, int chunk) {
+                                                                      int vdim, float scale, int chunk, AttnExtra x) {
   __shared__ float sm_m[kGqaWarps], sm_l[kGqaWarps];
   extern __shared__ float sm_acc[];  // [warps][vdim]
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G), lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int p = pos[t], lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int p = pos[t], lo = first_visible(p, chunk, x.window);
+  const float slope = head_slope(x.slope_log2, h, H);
   const int* pg = pages + page_off[req[t]];
   const int tok = G * (dim + vdim);
   float qr[kGqaMaxPerLane], acc[kGqaMaxPerLane];
@@ -91,7 +128,7 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
       const int d = lane + 32 * i;
       if (d < dim) s = fmaf(qr[i], to_f(kr[d]), s);
     }
-    s = warp_sum(s);
+    s = shape_score(warp_sum(s), x.softcap, slope, p - j);
     const float mn = fmaxf(m, s), c = expf(m - mn), e = expf(s - mn);
     l = l * c + e;
 #pragma unroll
@@ -126,7 +163,9 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < kGqaWarps; ++w) o += sm_acc[w * vdim + d] * cw[w];
-    out[((size_t)t * H + h) * vdim + d] = from_f<E>(o / den);
+    o /= den;
+    if (x.gate) o *= 1.f / (1.f + expf(-to_f(static_cast<const E*>(x.gate)[(size_t)t * x.gate_ld + h * vdim + d])));
+    out[((size_t)t * H + h) * vdim + d] = from_f<E>(o);
   }
 }
 
@@ -142,7 +181,7 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
                                                                const int* __restrict__ pos, const int* __restrict__ req,
                                                                const int* __restrict__ page_off, const int* __restrict__ pages,
                                                                bf16* __restrict__ out, long page_stride, int page_size, int T, int H, int G,
-                                                               float scale, int chunk) {
+                                                               float scale, int chunk, AttnExtra x) {
   constexpr int LDK = DQ + 8, LDV = DV + 8;
   extern __shared__ __align__(16) unsigned char am_smem[];  // two stages of [keys][LDK] K and [keys][LDV] V
   bf16* const Ks0 = reinterpret_cast<bf16*>(am_smem);
@@ -162,7 +201,8 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
   // this warp's rows: r0 = warp * 16 + gq and r0 + 8
   const int ra = warp * 16 + gq, rb = ra + 8;
   const int req_a = s_req[ra], req_b = s_req[rb], pos_a = s_pos[ra], pos_b = s_pos[rb];
-  const int lo_a = chunk > 0 && pos_a >= 0 ? (pos_a / chunk) * chunk : 0, lo_b = chunk > 0 && pos_b >= 0 ? (pos_b / chunk) * chunk : 0;
+  const int lo_a = pos_a >= 0 ? first_visible(pos_a, chunk, x.window) : 0, lo_b = pos_b >= 0 ? first_visible(pos_b, chunk, x.window) : 0;
+  const float slope = head_slope(x.slope_log2, h, H);
   // Q fragments (A operand, row-major 16 x DQ)
   uint32_t qa[DQ / 16][4];
 #pragma unroll
@@ -184,7 +224,7 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
     int r_last = r_first;
     while (r_last + 1 < kAmRows && s_req[r_last + 1] == rq) ++r_last;
     const int p_min = s_pos[r_first], p_max = s_pos[r_last];
-    const int k_lo = chunk > 0 ? (p_min / chunk) * chunk : 0;
+    const int k_lo = first_visible(p_min, chunk, x.window);
     const int* pg = pages + page_off[rq];
     // stage `buf` <- keys k0 .. k0 + 63 of this request (cp.async; rows outside [k_lo, p_max] are zero-filled)
     auto load = [&](int k0, int buf) {
@@ -234,7 +274,7 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
           const int j = k0 + ni * 8 + 2 * tq + (e & 1);
           const bool top = e < 2;
           const bool ok = top ? (on_a && j <= pos_a && j >= lo_a) : (on_b && j <= pos_b && j >= lo_b);
-          const float v = ok ? s[ni][e] * scale : -INFINITY;
+          const float v = ok ? shape_score(s[ni][e] * scale, x.softcap, slope, (top ? pos_a : pos_b) - j) : -INFINITY;
           s[ni][e] = v;
           if (top) mx_a = fmaxf(mx_a, v);
           else mx_b = fmaxf(mx_b, v);
@@ -293,14 +333,21 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
 #pragma unroll
   for (int ni = 0; ni < DV / 8; ++ni) {
     const int c = ni * 8 + 2 * tq;
-    if (req_a >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + ra) * H + h) * DV + c) = pack_bf16(oa[ni][0] * i_a, oa[ni][1] * i_a);
-    if (req_b >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + rb) * H + h) * DV + c) = pack_bf16(oa[ni][2] * i_b, oa[ni][3] * i_b);
+    float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
+    if (x.gate) {
+      const bf16* ga = static_cast<const bf16*>(x.gate) + (size_t)(t0 + ra) * x.gate_ld + h * DV + c;
+      const bf16* gb = static_cast<const bf16*>(x.gate) + (size_t)(t0 + rb) * x.gate_ld + h * DV + c;
+      if (req_a >= 0) g0 = 1.f / (1.f + expf(-bf2f(ga[0]))), g1 = 1.f / (1.f + expf(-bf2f(ga[1])));
+      if (req_b >= 0) g2 = 1.f / (1.f + expf(-bf2f(gb[0]))), g3 = 1.f / (1.f + expf(-bf2f(gb[1])));
+    }
+    if (req_a >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + ra) * H + h) * DV + c) = pack_bf16(oa[ni][0] * i_a * g0, oa[ni][1] * i_a * g1);
+    if (req_b >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + rb) * H + h) * DV + c) = pack_bf16(oa[ni][2] * i_b * g2, oa[ni][3] * i_b * g3);
   }
 }
 
 template <int DQ, int DV>
 static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off, const int* pages,
-                           bf16* out, long page_stride, int page_size, int T, int H, int G, float scale, int chunk, cudaStream_t st) {
+                           bf16* out, long page_stride, int page_size, int T, int H, int G, float scale, int chunk, AttnExtra x, cudaStream_t st) {
   const size_t smem = (size_t)2 * kAmKeys * (DQ + 8 + DV + 8) * sizeof(bf16);
   static bool attr_set = false;  // per template instance
   if (!attr_set) {
@@ -308,7 +355,7 @@ static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, c
     attr_set = true;
   }
   launch(gqa_attention_mma_kernel<DQ, DV>, dim3((T + kAmRows - 1) / kAmRows, H), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out,
-         page_stride, page_size, T, H, G, scale, chunk);
+         page_stride, page_size, T, H, G, scale, chunk, x);
 }
 
 }  // namespace pk
@@ -318,6 +365,14 @@ using namespace pk;
 extern "C" int pk_gqa_rope_append(const void* qkv, int ld, const void* bias, const int* positions, const int* req, const int* page_off,
                                   const int* pages, void* q_out, void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim,
                                   int vdim, int dims, int interleaved, const float* freq, float mag, int tokens, int f32, pk_stream st) {
+  return pk_gqa_rope_append_ex(qkv, ld, bias, positions, req, page_off, pages, q_out, cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims,
+                               interleaved, freq, mag, 0.f, tokens, f32, st);
+}
+
+extern "C" int pk_gqa_rope_append_ex(const void* qkv, int ld, const void* bias, const int* positions, const int* req, const int* page_off,
+                                     const int* pages, void* q_out, void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim,
+                                     int vdim, int dims, int interleaved, const float* freq, float mag, float value_norm_eps, int tokens, int f32,
+                                     pk_stream st) {
   if (!qkv || !positions || !req || !page_off || !pages || !q_out || !cache || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       dim <= 0 || vdim <= 0 || dims < 0 || dims > dim || (dims & 1) || (dims > 0 && !freq) || page_size <= 0)
     return -1;
@@ -326,27 +381,40 @@ extern "C" int pk_gqa_rope_append(const void* qkv, int ld, const void* bias, con
   const dim3 grid(tokens, tokens >= 128 ? 1 : std::min((n_all + 255) / 256, 16));
   if (f32)
     launch(gqa_rope_append_kernel<float>, grid, dim3(256), 0, st, true, (const float*)qkv, ld, (const float*)bias, positions, req, page_off, pages,
-           (float*)q_out, (float*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
+           (float*)q_out, (float*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag, value_norm_eps);
   else
     launch(gqa_rope_append_kernel<bf16>, grid, dim3(256), 0, st, true, (const bf16*)qkv, ld, (const bf16*)bias, positions, req, page_off, pages,
-           (bf16*)q_out, (bf16*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
+           (bf16*)q_out, (bf16*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag, value_norm_eps);
   return (int)cudaGetLastError();
 }
 
 extern "C" int pk_gqa_attention(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                                 const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim,
                                 int vdim, float scale, int chunk, int f32, pk_stream st) {
+  return pk_gqa_attention_ex(q, cache, sink, positions, req, page_off, pages, out, page_stride, page_size, tokens, heads, kv_heads, dim, vdim, scale,
+                             chunk, nullptr, f32, st);
+}
+
+extern "C" int pk_gqa_attention_ex(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                                   const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim,
+                                   int vdim, float scale, int chunk, const pk_attn_extra* extra, int f32, pk_stream st) {
   if (!q || !cache || !positions || !req || !page_off || !pages || !out || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       dim <= 0 || vdim <= 0 || chunk < 0 || page_size <= 0)
     return -1;
+  AttnExtra x{0, 0.f, 0.f, nullptr, 0};
+  if (extra) {
+    if (extra->window < 0 || extra->softcap < 0.f || extra->slope_log2 < 0.f) return -1;
+    x = AttnExtra{extra->window, extra->softcap, extra->slope_log2, extra->gate, extra->gate_ld};
+  }
   if (dim > 32 * kGqaMaxPerLane || vdim > 32 * kGqaMaxPerLane) return -2;
   const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                        page_stride % 8 == 0;
-  if (!f32 && tokens >= 32 && aligned && dim == vdim && (dim == 64 || dim == 128 || dim == 32)) {
+  if (!f32 && tokens >= 32 && aligned && dim == vdim && (dim == 64 || dim == 128 || dim == 32 || dim == 96) && (dim * kv_heads) % 8 == 0) {
 #define PK_GQA_MMA(D) \
-  launch_gqa_mma<D, D>((const bf16*)q, (const bf16*)cache, (const bf16*)sink, positions, req, page_off, pages, (bf16*)out, page_stride, page_size, tokens, heads, kv_heads, scale, chunk, st)
+  launch_gqa_mma<D, D>((const bf16*)q, (const bf16*)cache, (const bf16*)sink, positions, req, page_off, pages, (bf16*)out, page_stride, page_size, tokens, heads, kv_heads, scale, chunk, x, st)
     if (dim == 32) PK_GQA_MMA(32);
     else if (dim == 64) PK_GQA_MMA(64);
+    else if (dim == 96) PK_GQA_MMA(96);
     else PK_GQA_MMA(128);
 #undef PK_GQA_MMA
     return (int)cudaGetLastError();
@@ -354,9 +422,9 @@ extern "C" int pk_gqa_attention(const void* q, const void* cache, const void* si
   const size_t smem = (size_t)kGqaWarps * vdim * sizeof(float);
   if (f32)
     launch(gqa_attention_kernel<float>, dim3(tokens, heads), dim3(kGqaWarps * 32), smem, st, true, (const float*)q, (const float*)cache, (const float*)sink,
-           positions, req, page_off, pages, (float*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk);
+           positions, req, page_off, pages, (float*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk, x);
   else
     launch(gqa_attention_kernel<bf16>, dim3(tokens, heads), dim3(kGqaWarps * 32), smem, st, true, (const bf16*)q, (const bf16*)cache, (const bf16*)sink,
-           positions, req, page_off, pages, (bf16*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk);
+           positions, req, page_off, pages, (bf16*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk, x);
   return (int)cudaGetLastError();
 }

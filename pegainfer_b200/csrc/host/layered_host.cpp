@@ -1,11 +1,14 @@
-// C++ host of the decoder designs whose checkpoint configuration lists the layers one by one (Vamadra, Risolorn), on an fp32
-// residual stream.  A layer is a mixer plus an optional feed-forward, put together in one of two block forms:
+// C++ host of the decoder designs whose checkpoint configuration lists the layers one by one (Vamadra, Risolorn, Nagosun), on an
+// fp32 residual stream.  A layer is a mixer plus an optional feed-forward, put together in one of three block forms:
 //   block 0  sequential sublayers with the norm on each sublayer's OUTPUT:  x += norm(mixer(x));  x += norm(ff(x))
 //   block 1  parallel sublayers under one Dynamic-Tanh pre-norm:            h = dyt(x);  x += mixer(h) + ff(h)
+//   block 2  "sandwich": a grouped RMS norm before AND after each sublayer, the sublayer's result gated by a logistic
+//            projection of its input, the sum scaled:  h = gn(x); x += m * gn(f(h) * logistic(W_rg h + b))   (mixers 0 and 1)
 // Mixers: 0 latent attention (compressed paged cache, shared rotated key part, per-head sink, logistic output gate, optional
 // reuse of an earlier layer's cache); 1 grouped-query attention with biases, rotary embedding from a frequency table, a
-// chunk-local causal mask and a sink, over a paged K/V cache; 2 gated delta rule behind short causal convolutions; 3 xLSTM
-// matrix memory.  Mixers 2 and 3 keep an fp32 state per request in numbered state slots.  Feed-forward: dense SwiGLU or a
+// chunk-local causal mask and a sink, over a paged K/V cache (block 2 adds: sliding window, score soft cap, linear distance
+// bias, unit-RMS cached values, a sink of score zero, an element-wise output gate); 2 gated delta rule behind short causal
+// convolutions; 3 xLSTM matrix memory.  Mixers 2 and 3 keep an fp32 state per request in numbered state slots.  Feed-forward: dense SwiGLU or a
 // mixture of experts (softmax or logistic router, relu^2 or gated-SiLU experts).
 //
 // Same structure as the other hosts in this folder: kernels are reached only through the C ABI
@@ -55,13 +58,24 @@ struct LayerCfg {  // mirrored by ctypes in pegainfer_b200/vamadra.py
   float gate_cap;            // 3: soft cap of the log gates
   int router_kind;           // 0 softmax scores, best expert per group, renormalised; 1 logistic scores + choice correction, two best per group, plain
   int expert_act;            // 0 relu^2, 1 gated SiLU
+  // options read by block 2 (all off when zero)
+  int window;                // attention (0, 1): a query at position p sees keys p - window + 1 .. p
+  float softcap;             // 1: scaled score <- softcap * tanh(score / softcap)
+  float slope_log2;          // 1: head h subtracts 2^(-slope_log2 (h + 1) / heads) * distance from the score
+  int value_norm;            // 1: cached values are divided by their root mean square per head (eps of the model, no weight)
+  int sink_kind;             // 0 learned per-head sink 'mix.sink', 1 none, 2 a sink of score zero (one added to the softmax denominator)
+  int out_gate;              // 1: 1 = heads' outputs times logistic(W_g h) element by element ('mix.g' [heads * vdim, width])
+  int proj_bias;             // 1: q, k, v and o projections carry biases ('.b')
 };
 struct ModelCfg {
   int vocab, width, n_layers;
   float eps;
   int f32, page_size, num_pages, max_requests, device, enable_pdl;
-  int block_kind;  // 0 sequential sublayers, offset RMS norm on their outputs; 1 parallel sublayers under a Dynamic-Tanh pre-norm
+  int block_kind;  // 0 sequential sublayers, offset RMS norm on their outputs; 1 parallel sublayers under a Dynamic-Tanh pre-norm; 2 sandwich
   float embed_scale, logit_scale;
+  int norm_groups;        // block 2: parts of a row that are normed separately
+  float residual_mult;    // block 2: multiplier of every sublayer's normed result
+  int gated_residual;     // block 2: sublayer results times logistic(W_rg h + b) ('rg1' / 'rg2') before their norm
 };
 
 struct Lib {
@@ -77,8 +91,21 @@ struct Lib {
 #define PV_BLOCK1(X)                                                                                                                        \
   X(pk_res32_embed_scaled) X(pk_res32_add_dyt) X(pk_res32_dyt_rows) X(pk_gqa_rope_append) X(pk_gqa_attention) X(pk_causal_conv_silu)       \
   X(pk_gated_delta_seq) X(pk_mlstm_seq) X(pk_head_norm_gate) X(pk_router_topk_ex)
+#define PV_BLOCK2(X)                                                                                                                        \
+  X(pk_res32_embed_gnorm) X(pk_res32_gated_gnorm_add) X(pk_res32_gnorm_rows) X(pk_gqa_rope_append_ex) X(pk_gqa_attention_ex) X(pk_rope_slice_ex)   \
+  X(pk_latent_kv_append_ex) X(pk_latent_attention_ex) X(pk_act) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu) X(pk_b200_gemm_segments)
 #define PV_FN(name) decltype(&::name) name = nullptr;
   PV_COMMON(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN)
+  // block 2 shares pk_act / pk_b200_gemv_fused / pk_b200_gemm_swiglu with block 0
+  decltype(&::pk_res32_embed_gnorm) pk_res32_embed_gnorm = nullptr;
+  decltype(&::pk_res32_gated_gnorm_add) pk_res32_gated_gnorm_add = nullptr;
+  decltype(&::pk_res32_gnorm_rows) pk_res32_gnorm_rows = nullptr;
+  decltype(&::pk_gqa_rope_append_ex) pk_gqa_rope_append_ex = nullptr;
+  decltype(&::pk_gqa_attention_ex) pk_gqa_attention_ex = nullptr;
+  decltype(&::pk_rope_slice_ex) pk_rope_slice_ex = nullptr;
+  decltype(&::pk_latent_kv_append_ex) pk_latent_kv_append_ex = nullptr;
+  decltype(&::pk_latent_attention_ex) pk_latent_attention_ex = nullptr;
+  decltype(&::pk_b200_gemm_segments) pk_b200_gemm_segments = nullptr;
 #undef PV_FN
   // a library built for one design need not hold the other block form's kernels: only what `block_kind` runs is required
   std::string load(const std::string& p, int block_kind) {
@@ -91,8 +118,10 @@ struct Lib {
     PV_COMMON(PV_REQ)
     if (block_kind == 0) {
       PV_BLOCK0(PV_REQ)
-    } else {
+    } else if (block_kind == 1) {
       PV_BLOCK1(PV_REQ)
+    } else {
+      PV_BLOCK2(PV_REQ)
     }
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
@@ -116,6 +145,7 @@ struct Layer {
   Mat e_up, e_down, router, s_up, s_down, s_gate;          // experts stacked [experts * ff, width] / [experts * width, ff]
   // mixers 1-3 / block 1: stacked projections [q | k | v (| gate)], their bias, the few-row fp32 projections [router | za | zb]
   Mat nb, qkv, qkv_bias, small, conv_w, hnorm;
+  Mat norm1b, norm2b, o_bias, rg1_bias, rg2, rg2_bias;    // block 2: post-norms, output bias, gates of the sublayer results (rg1 is stacked into qkv)
   DeviceBuf alpha32, corr32, p0_32, p1_32;                 // float copies of small parameter vectors (made in finalize)
   Mat alpha, corr, p0, p1;
   int64_t state_off = 0;                                   // float offset of the layer's block inside a state slot
@@ -135,6 +165,9 @@ struct Model {
   int es = 2;  // element size
   Mat embed, head, final_norm, final_b, final_alpha;
   DeviceBuf final_alpha32;
+  Mat embed_norm;                // block 2: norm of the embedding
+  DeviceBuf zero_sink;           // block 2: [heads] zeros, the sink of score zero
+  DeviceBuf rgbuf;               // block 2: gate pre-activations [tokens, width]
   DeviceBuf cache, state;        // paged cache pool; recurrent state, one slot per request id
   int64_t slot_stride = 0;       // floats per state slot
   std::vector<char> fresh;       // request slot allocated and not stepped yet: its state is zeroed before the first step
@@ -194,8 +227,11 @@ struct Model {
   bool skinny(const Mat& W, float* out, int T, const char* what, const float* in32 = nullptr);
   bool put_rows(Mat& m, int rows, int cols, int row0, int row_step, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols);
   bool to_f32(const Mat& m, DeviceBuf* out);
+  bool put_uk(Layer& L, const void* data, const std::string& name, int rows, int cols);
   bool run_experts(Layer& L, int T, const void* shared);
   bool run_parallel_layer(int li, int T, const int* M, int n);
+  bool run_sandwich_layer(int li, int T, int max_kv, const int* M, int n);
+  bool lin_segments(const Mat& W, const void* X, void* const* Y, const int* seg_rows, int N);
   bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
   bool forward(int T, int n, int n_rows, int max_kv, int want_sample);
   bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
@@ -213,7 +249,8 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
   c = mc;
   es = c.f32 ? 4 : 2;
   if (c.vocab <= 0 || c.width <= 0 || c.n_layers <= 0) return fail("vocab, width and the number of layers must be positive");
-  if (c.block_kind < 0 || c.block_kind > 1) return fail("unknown block form");
+  if (c.block_kind < 0 || c.block_kind > 2) return fail("unknown block form");
+  if (c.block_kind == 2 && (c.norm_groups <= 0 || c.width % c.norm_groups)) return fail("norm.groups must divide the width");
   if (c.page_size <= 0) c.page_size = 16;
   if (c.max_requests <= 0) c.max_requests = 4;
   layers.resize(c.n_layers);
@@ -223,7 +260,8 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     L.c = lc[i];
     const LayerCfg& a = L.c;
     if (a.mixer_kind < 0 || a.mixer_kind > 3) return fail(lname(i, "mixer: unknown kind"));
-    if ((a.mixer_kind == 0) != (c.block_kind == 0)) return fail(lname(i, "mixer: not available in this block form"));
+    if (c.block_kind == 2 ? a.mixer_kind > 1 : (a.mixer_kind == 0) != (c.block_kind == 0)) return fail(lname(i, "mixer: not available in this block form"));
+    if (a.window < 0 || a.softcap < 0.f || a.slope_log2 < 0.f) return fail(lname(i, "mixer: mask.size, softcap and the bias slope must not be negative"));
     if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0) return fail(lname(i, "mixer: sizes must be positive"));
     if (a.mixer_kind == 0) {
       if (a.kv_rank <= 0 || a.rot_dim < 0) return fail(lname(i, "mixer: sizes must be positive"));
@@ -255,7 +293,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
         L.cache_off = off;
         off += (int64_t)c.page_size * a.kv_heads * (a.dim + a.vdim);
         off = (off + 7) / 8 * 8;  // every layer's block starts 16-byte aligned in both element types
-        mx_big = std::max(mx_big, nqk + a.kv_heads * a.vdim);
+        mx_big = std::max(mx_big, nqk + a.kv_heads * a.vdim + (c.block_kind == 2 ? (a.out_gate ? a.heads * a.vdim : 0) + (c.gated_residual ? c.width : 0) : 0));
         mx_q = std::max(mx_q, a.heads * a.dim);
       } else {
         if (a.mixer_kind == 2 && a.conv <= 0) return fail(lname(i, "mixer: conv must be positive"));
@@ -271,6 +309,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     }
     if (a.mlp_kind == 1 && a.ff <= 0) return fail(lname(i, "mlp: ff must be positive"));
     if (c.block_kind == 1 && a.mlp_kind == 1) return fail(lname(i, "mlp: the parallel block form has no dense feed-forward"));
+    if (c.block_kind == 2 && a.mlp_kind == 2) return fail(lname(i, "mlp: the sandwich block form has no mixture of experts"));
     if (a.mlp_kind == 2) {
       if (a.experts <= 0 || a.top <= 0 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
           a.top > a.keep * (a.experts / a.groups))
@@ -326,6 +365,20 @@ bool Model::put_rows(Mat& m, int rows, int cols, int row0, int row_step, const v
             name.c_str());
 }
 
+// W_uk [heads * dim, rank] as stored, and a second copy with the contraction axis of the query fold contiguous: [head][rank][dim]
+bool Model::put_uk(Layer& L, const void* data, const std::string& name, int rows, int cols) {
+  const LayerCfg& a = L.c;
+  if (!put(L.uk, a.heads * a.dim, a.kv_rank, 0, data, a.heads * a.dim, name, rows, cols)) return false;
+  const size_t n = (size_t)a.heads * a.dim * a.kv_rank;
+  std::vector<char> src(n * es), dst(n * es);
+  if (!cu(cudaMemcpy(src.data(), data, n * es, cudaMemcpyDefault), name.c_str())) return false;
+  for (int h = 0; h < a.heads; ++h)
+    for (int d = 0; d < a.dim; ++d)
+      for (int r = 0; r < a.kv_rank; ++r)
+        memcpy(&dst[(((size_t)h * a.kv_rank + r) * a.dim + d) * es], &src[(((size_t)h * a.dim + d) * a.kv_rank + r) * es], es);
+  return put(L.uk_t, a.heads * a.kv_rank, a.dim, 0, dst.data(), a.heads * a.kv_rank, name, a.heads * a.kv_rank, a.dim);
+}
+
 // float copy of a small parameter vector that enters fp32 arithmetic only
 bool Model::to_f32(const Mat& m, DeviceBuf* out) {
   const long n = (long)m.rows * m.cols;
@@ -338,6 +391,7 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
   if ((is_f32 != 0) != (c.f32 != 0)) return fail(name + ": element type differs from the model's");
   const int W = c.width;
   if (name == "embed") return put(embed, c.vocab, W, 0, data, c.vocab, name, rows, cols);
+  if (c.block_kind == 2 && name == "embed.norm") return put(embed_norm, 1, W, 0, data, 1, name, rows, cols);
   if (name == "head") return put(head, c.vocab, W, 0, data, c.vocab, name, rows, cols);
   if (name == "final.norm") return put(final_norm, 1, W, 0, data, 1, name, rows, cols);
   if (c.block_kind == 1 && name == "final.norm.b") return put(final_b, 1, W, 0, data, 1, name, rows, cols);
@@ -409,24 +463,56 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
     if (ok) L.got.insert(sub);
     return ok;
   }
+  if (c.block_kind == 2) {
+    // sandwich block: [q | k | v (| g) (| rg1)] (attention) or [q | dkv (| rg1)] (latent attention) stacked into one projection
+    const int H = a.heads, G = a.kv_heads, mk = a.mixer_kind, rg = c.gated_residual ? W : 0;
+    const int nq = mk == 1 ? H * a.dim : H * (a.dim + a.rot_dim), nk = mk == 1 ? G * a.dim : a.kv_rank + a.rot_dim, nv = mk == 1 ? G * a.vdim : 0;
+    const int ng = mk == 1 && a.out_gate ? H * a.vdim : 0, nbig = nq + nk + nv + ng + rg;
+    auto vec = [&](Mat& m, int n, int total, int at) {  // a vector stored as a slice of a [1, total] row
+      if (rows != 1 || cols != n) return fail(name + ": shape does not match the configuration");
+      if (!m.d.ptr) {
+        m.rows = 1;
+        m.cols = total;
+        if (!m.d.alloc_zeros((size_t)total * es)) return fail("allocation failed for " + name);
+      }
+      return cu(cudaMemcpy((char*)m.d.ptr + (size_t)at * es, data, (size_t)n * es, cudaMemcpyDefault), name.c_str());
+    };
+    if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
+    else if (sub == "norm1b") ok = put(L.norm1b, 1, W, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind && sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind && sub == "norm2b") ok = put(L.norm2b, 1, W, 0, data, 1, name, rows, cols);
+    else if (sub == "mix.q") ok = put(L.qkv, nbig, W, 0, data, nq, name, rows, cols);
+    else if (mk == 1 && sub == "mix.k") ok = put(L.qkv, nbig, W, nq, data, nk, name, rows, cols);
+    else if (mk == 1 && sub == "mix.v") ok = put(L.qkv, nbig, W, nq + nk, data, nv, name, rows, cols);
+    else if (ng && sub == "mix.g") ok = put(L.qkv, nbig, W, nq + nk + nv, data, ng, name, rows, cols);
+    else if (rg && sub == "rg1") ok = put(L.qkv, nbig, W, nq + nk + nv + ng, data, W, name, rows, cols);
+    else if (rg && sub == "rg1.b") ok = put(L.rg1_bias, 1, W, 0, data, 1, name, rows, cols);
+    else if (rg && a.mlp_kind && sub == "rg2") ok = put(L.rg2, W, W, 0, data, W, name, rows, cols);
+    else if (rg && a.mlp_kind && sub == "rg2.b") ok = put(L.rg2_bias, 1, W, 0, data, 1, name, rows, cols);
+    else if (mk == 1 && a.proj_bias && sub == "mix.q.b") ok = vec(L.qkv_bias, nq, nq + nk + nv, 0);
+    else if (mk == 1 && a.proj_bias && sub == "mix.k.b") ok = vec(L.qkv_bias, nk, nq + nk + nv, nq);
+    else if (mk == 1 && a.proj_bias && sub == "mix.v.b") ok = vec(L.qkv_bias, nv, nq + nk + nv, nq + nk);
+    else if (mk == 1 && a.proj_bias && sub == "mix.o.b") ok = put(L.o_bias, 1, W, 0, data, 1, name, rows, cols);
+    else if (mk == 1 && a.sink_kind == 0 && sub == "mix.sink") ok = put(L.sink, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 0 && sub == "mix.dkv") ok = put(L.qkv, nbig, W, nq, data, nk, name, rows, cols);
+    else if (mk == 0 && sub == "mix.dkv.norm") ok = put(L.dkv_norm, 1, a.kv_rank, 0, data, 1, name, rows, cols);
+    else if (mk == 0 && sub == "mix.uk") ok = put_uk(L, data, name, rows, cols);
+    else if (mk == 0 && sub == "mix.uv") ok = put(L.uv, H * a.vdim, a.kv_rank, 0, data, H * a.vdim, name, rows, cols);
+    else if (mk == 0 && a.sink_kind == 0 && sub == "mix.sink") ok = put(L.sink, 1, H, 0, data, 1, name, rows, cols);
+    else if (sub == "mix.o") ok = put(L.o, W, H * a.vdim, 0, data, W, name, rows, cols);
+    else if (a.mlp_kind == 1 && sub == "mlp.gate") ok = put(L.gate_up, 2 * a.ff, W, 0, data, a.ff, name, rows, cols);
+    else if (a.mlp_kind == 1 && sub == "mlp.up") ok = put(L.gate_up, 2 * a.ff, W, a.ff, data, a.ff, name, rows, cols);
+    else if (a.mlp_kind == 1 && sub == "mlp.down") ok = put(L.down, W, a.ff, 0, data, W, name, rows, cols);
+    else return fail("unknown tensor " + name + " for the configuration of layer " + std::to_string(li));
+    if (ok) L.got.insert(sub);
+    return ok;
+  }
   if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "mix.q") ok = put(L.q, a.heads * (a.dim + a.rot_dim), W, 0, data, a.heads * (a.dim + a.rot_dim), name, rows, cols);
   else if (sub == "mix.dkv" && a.kv_from < 0) ok = put(L.dkv, a.kv_rank + a.rot_dim, W, 0, data, a.kv_rank + a.rot_dim, name, rows, cols);
   else if (sub == "mix.dkv.norm" && a.kv_from < 0) ok = put(L.dkv_norm, 1, a.kv_rank, 0, data, 1, name, rows, cols);
-  else if (sub == "mix.uk") {
-    ok = put(L.uk, a.heads * a.dim, a.kv_rank, 0, data, a.heads * a.dim, name, rows, cols);
-    if (ok) {  // the query fold contracts over `dim`: keep a copy with that axis contiguous, [head][rank][dim]
-      const size_t n = (size_t)a.heads * a.dim * a.kv_rank;
-      std::vector<char> src(n * es), dst(n * es);
-      ok = cu(cudaMemcpy(src.data(), data, n * es, cudaMemcpyDefault), name.c_str());
-      for (int h = 0; h < a.heads && ok; ++h)
-        for (int d = 0; d < a.dim; ++d)
-          for (int r = 0; r < a.kv_rank; ++r)
-            memcpy(&dst[(((size_t)h * a.kv_rank + r) * a.dim + d) * es], &src[(((size_t)h * a.dim + d) * a.kv_rank + r) * es], es);
-      ok = ok && put(L.uk_t, a.heads * a.kv_rank, a.dim, 0, dst.data(), a.heads * a.kv_rank, name, a.heads * a.kv_rank, a.dim);
-    }
-  }
+  else if (sub == "mix.uk") ok = put_uk(L, data, name, rows, cols);
   else if (sub == "mix.uv") ok = put(L.uv, a.heads * a.vdim, a.kv_rank, 0, data, a.heads * a.vdim, name, rows, cols);
   else if (sub == "mix.sink") ok = put(L.sink, 1, a.heads, 0, data, 1, name, rows, cols);
   else if (sub == "mix.g") ok = put(L.g, a.heads, W, 0, data, a.heads, name, rows, cols);
@@ -479,6 +565,8 @@ static void rotary_table(const LayerCfg& a, std::vector<float>* f, float* mag) {
 
 bool Model::finalize() {
   if (!embed.d.ptr || !head.d.ptr || !final_norm.d.ptr) return fail("embed / head / final.norm missing");
+  if (c.block_kind == 2 && !embed_norm.d.ptr) return fail("embed.norm missing");
+  if (c.block_kind == 2 && !zero_sink.alloc_zeros((size_t)std::max(mx_h, 1) * es)) return fail("allocation failed");
   if (c.block_kind == 1 && (!final_b.d.ptr || !final_alpha.d.ptr || !to_f32(final_alpha, &final_alpha32))) return fail("final.norm.b / final.norm.alpha missing");
   if (slot_stride > 0 && !state.alloc_zeros((size_t)c.max_requests * slot_stride * 4)) return fail("state slot allocation failed");
   if (page_stride == 0) page_stride = 8;  // no layer keeps a paged cache: the pool only counts tokens
@@ -490,6 +578,16 @@ bool Model::finalize() {
       need = {"norm1", "mix.q", "mix.uk", "mix.uv", "mix.sink", "mix.g", "mix.o"};
       if (a.kv_from < 0) need.insert(need.end(), {"mix.dkv", "mix.dkv.norm"});
       if (a.mlp_kind) need.push_back("norm2");
+    } else if (c.block_kind == 2) {
+      need = {"norm1", "norm1b", "mix.q", "mix.o"};
+      if (a.mixer_kind == 1) need.insert(need.end(), {"mix.k", "mix.v"});
+      else need.insert(need.end(), {"mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv"});
+      if (a.mixer_kind == 1 && a.proj_bias) need.insert(need.end(), {"mix.q.b", "mix.k.b", "mix.v.b", "mix.o.b"});
+      if (a.mixer_kind == 1 && a.out_gate) need.push_back("mix.g");
+      if (a.sink_kind == 0) need.push_back("mix.sink");
+      if (c.gated_residual) need.insert(need.end(), {"rg1", "rg1.b"});
+      if (a.mlp_kind) need.insert(need.end(), {"norm2", "norm2b"});
+      if (a.mlp_kind && c.gated_residual) need.insert(need.end(), {"rg2", "rg2.b"});
     } else {
       need = {"norm1", "norm1.b", "norm1.alpha", "mix.q", "mix.k", "mix.v", "mix.o"};
       if (a.mixer_kind == 1) need.insert(need.end(), {"mix.q.b", "mix.k.b", "mix.v.b", "mix.sink"});
@@ -515,6 +613,7 @@ bool Model::finalize() {
       if (a.mixer_kind >= 2 && (!to_f32(L.p0, &L.p0_32) || !to_f32(L.p1, &L.p1_32))) return false;
       if (a.mixer_kind != 1) continue;  // only attention rotates
     }
+    if (c.block_kind == 2 && a.rot_dims == 0) continue;  // nothing rotates
     std::vector<float> f;
     rotary_table(a, &f, &L.mag);
     if (!L.freq.alloc_zeros(f.size() * 4) || !cu(cudaMemcpy(L.freq.ptr, f.data(), f.size() * 4, cudaMemcpyHostToDevice), "rotary table"))
@@ -553,6 +652,7 @@ bool Model::ensure_scratch(int T, int R) {
     if (ok && c.block_kind == 1)
       ok = h32.alloc_uninit(n * W * 4) && big.alloc_uninit(n * std::max(mx_big, 1) * es) && convo.alloc_uninit(n * std::max(mx_conv, 1) * es) &&
            zs.alloc_uninit(n * std::max(mx_small, 1) * 4) && orec.alloc_uninit(n * std::max(mx_ao, 1) * 4) && den.alloc_uninit(n * std::max(mx_h, 1) * 4);
+    if (ok && c.block_kind == 2) ok = big.alloc_uninit(n * std::max(mx_big, 1) * es) && rgbuf.alloc_uninit(n * W * es);
     if (ok && !c.f32 && (int)n >= kGroupedMinTokens) {  // bucketed experts for prompt portions
       long ws = 0;
       for (auto& L : layers)
@@ -749,6 +849,144 @@ bool Model::run_parallel_layer(int li, int T, const int* M, int n) {
   return true;
 }
 
+// One projection whose output rows fall into up to three segments, each written to its own packed buffer [N, seg_rows[i]]
+bool Model::lin_segments(const Mat& W, const void* X, void* const* Y, const int* seg_rows, int N) {
+  if (!c.f32 && N > 4) {
+    pk_bf16* ys[3] = {(pk_bf16*)Y[0], (pk_bf16*)Y[1], (pk_bf16*)Y[2]};
+    return rc(k.pk_b200_gemm_segments((const pk_bf16*)W.d.ptr, (const pk_bf16*)X, ys, seg_rows, W.rows, N, W.cols, st), "stacked projection");
+  }
+  if (!c.f32) {  // streaming GEMV with segmented output; shapes it does not take run one GEMV per segment below
+    pk_b200_gemv_args g{};
+    g.W = (const pk_bf16*)W.d.ptr;
+    g.X = (const pk_bf16*)X;
+    for (int i = 0; i < 3; ++i) {
+      g.Y[i] = (pk_bf16*)Y[i];
+      g.seg_rows[i] = seg_rows[i];
+    }
+    g.M = W.rows;
+    g.N = N;
+    g.K = W.cols;
+    if (k.pk_b200_gemv_fused(&g, st) == 0) return true;
+  }
+  int r0 = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (seg_rows[i] <= 0) continue;
+    const char* base = (const char*)W.d.ptr + (size_t)r0 * W.cols * es;
+    if (c.f32) {
+      if (!rc(k.pk_gemm_strided(X, base, Y[i], nullptr, N, seg_rows[i], W.cols, W.cols, 1, W.cols, seg_rows[i], 1, 0, 0, 0, 0, 0, 1, st), "stacked projection"))
+        return false;
+    } else {
+      k.gemm_cuda((const pk_bf16*)base, (const pk_bf16*)X, (pk_bf16*)Y[i], seg_rows[i], N, W.cols, st);
+    }
+    r0 += seg_rows[i];
+  }
+  return true;
+}
+
+// Sandwich block: on entry xa holds gnorm(x, norm1) of this layer; on exit x holds the layer's result and xa the next layer's
+// pre-norm (nothing after the last layer).
+bool Model::run_sandwich_layer(int li, int T, int max_kv, const int* M, int n) {
+  Layer& L = layers[li];
+  const LayerCfg& a = L.c;
+  const int W = c.width, f32 = c.f32, H = a.heads, G = a.kv_heads, mk = a.mixer_kind, rg = c.gated_residual ? W : 0;
+  const int *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T;
+  const int* d_pages = M + pages_at;
+  char* pool_base = (char*)cache.ptr + (size_t)L.cache_off * es;
+  const void* sink = a.sink_kind == 0 ? L.sink.d.ptr : a.sink_kind == 2 ? zero_sink.ptr : nullptr;
+  const void* gate1 = nullptr;  // pre-activation of the gate on the mixer's result
+  long gate1_ld = 0;
+  if (mk == 1) {
+    const int nq = H * a.dim, nk = G * a.dim, nv = G * a.vdim, ng = a.out_gate ? H * a.vdim : 0, nbig = nq + nk + nv + ng + rg;
+    if (!lin(L.qkv, xa.ptr, big.ptr, T)) return false;
+    if (!rc(k.pk_gqa_rope_append_ex(big.ptr, nbig, L.qkv_bias.d.ptr, d_pos, d_req, d_poff, d_pages, q.ptr, pool_base, page_stride, c.page_size, H, G, a.dim,
+                                    a.vdim, a.rot_dims, a.rot_interleaved, (const float*)L.freq.ptr, L.mag, a.value_norm ? c.eps : 0.f, T, f32, st),
+            "cache append"))
+      return false;
+    pk_attn_extra ex{};
+    ex.window = a.window;
+    ex.softcap = a.softcap;
+    ex.slope_log2 = a.slope_log2;
+    ex.gate = ng ? (const char*)big.ptr + (size_t)(nq + nk + nv) * es : nullptr;
+    ex.gate_ld = nbig;
+    if (!rc(k.pk_gqa_attention_ex(q.ptr, pool_base, sink, d_pos, d_req, d_poff, d_pages, ao.ptr, page_stride, c.page_size, T, H, G, a.dim, a.vdim, a.scale,
+                                  a.chunk, &ex, f32, st),
+            "attention"))
+      return false;
+    if (rg) {
+      gate1 = (const char*)big.ptr + (size_t)(nq + nk + nv + ng) * es;
+      gate1_ld = nbig;
+    }
+  } else {
+    const int r = a.kv_rank, rd = a.rot_dim, D = r + rd;
+    void* outs[3] = {q.ptr, dkv.ptr, rgbuf.ptr};
+    const int segs[3] = {H * (a.dim + rd), D, rg};
+    if (!lin_segments(L.qkv, xa.ptr, outs, segs, T)) return false;
+    if (!rc(k.pk_latent_kv_append_ex(dkv.ptr, L.dkv_norm.d.ptr, d_pos, d_req, d_poff, d_pages, pool_base, page_stride, c.page_size, r, rd, a.rot_dims,
+                                     a.rot_interleaved, (const float*)L.freq.ptr, L.mag, c.eps, T, f32, st),
+            "latent cache append"))
+      return false;
+    // fold the unrotated query onto the latent (per head: qa[:, :r] = q_unrotated W_uk[h]), rotate the other part beside it
+    if (!rc(k.pk_gemm_strided(q.ptr, L.uk_t.d.ptr, qa.ptr, nullptr, T, r, a.dim, (long)H * (a.dim + rd), 1, a.dim, (long)H * D, H, a.dim + rd,
+                              (long)a.dim * r, D, 0, 0, f32, st),
+            "query fold"))
+      return false;
+    if (rd > 0 && !rc(k.pk_rope_slice_ex(q.ptr, qa.ptr, d_pos, (const float*)L.freq.ptr, L.mag, T, H, a.dim + rd, a.dim, D, r, rd, a.rot_dims, a.rot_interleaved,
+                                         f32, st),
+                      "query rotation"))
+      return false;
+    if (!rc(k.pk_latent_attention_ex(qa.ptr, pool_base, sink, d_pos, d_req, d_poff, d_pages, olat.ptr, page_stride, c.page_size, T, H, r, rd, a.scale, a.window,
+                                     max_kv, f32, st),
+            "latent attention"))
+      return false;
+    if (!rc(k.pk_gemm_strided(olat.ptr, L.uv.d.ptr, ao.ptr, nullptr, T, a.vdim, r, (long)H * r, 1, r, (long)H * a.vdim, H, r, (long)a.vdim * r, a.vdim, 0, 0, f32,
+                              st),
+            "value expansion"))
+      return false;
+    if (rg) {
+      gate1 = rgbuf.ptr;
+      gate1_ld = W;
+    }
+  }
+  if (!lin(L.o, ao.ptr, mix.ptr, T)) return false;
+  const Layer* next = li + 1 < c.n_layers ? &layers[li + 1] : nullptr;
+  const void* after_mixer = a.mlp_kind ? L.norm2.d.ptr : next ? next->norm1.d.ptr : nullptr;
+  if (!rc(k.pk_res32_gated_gnorm_add(mix.ptr, f32, L.o_bias.d.ptr, gate1, gate1_ld, gate1 ? L.rg1_bias.d.ptr : nullptr, L.norm1b.d.ptr, c.residual_mult,
+                                     (float*)x.ptr, after_mixer, xa.ptr, W, c.norm_groups, c.eps, T, f32, st),
+          "mixer result: gate, norm, residual"))
+    return false;
+  if (a.mlp_kind == 1) {
+    // gate | up projection with the SwiGLU activation in its epilogue where the library has it (as in the sequential block)
+    bool fused = false;
+    if (!f32 && T <= 4) {
+      pk_b200_gemv_args g{};
+      g.W = (const pk_bf16*)L.gate_up.d.ptr;
+      g.X = (const pk_bf16*)xa.ptr;
+      g.Y[0] = (pk_bf16*)act.ptr;
+      g.seg_rows[0] = a.ff;
+      g.M = a.ff;
+      g.N = T;
+      g.K = W;
+      g.epi = 1;
+      fused = k.pk_b200_gemv_fused(&g, st) == 0;
+    } else if (!f32) {
+      fused = k.pk_b200_gemm_swiglu((const pk_bf16*)L.gate_up.d.ptr, (const pk_bf16*)xa.ptr, (pk_bf16*)act.ptr, a.ff, T, W, st) == 0;
+    }
+    if (!fused) {
+      if (!lin(L.gate_up, xa.ptr, gu.ptr, T)) return false;
+      if (!rc(k.pk_act(gu.ptr, act.ptr, a.ff, T, 0, f32, st), "SwiGLU")) return false;
+    }
+    if (rg && !lin(L.rg2, xa.ptr, rgbuf.ptr, T)) return false;
+    if (!lin(L.down, act.ptr, mix.ptr, T)) return false;
+    if (!rc(k.pk_res32_gated_gnorm_add(mix.ptr, f32, nullptr, rg ? rgbuf.ptr : nullptr, W, rg ? L.rg2_bias.d.ptr : nullptr, L.norm2b.d.ptr, c.residual_mult,
+                                       (float*)x.ptr, next ? next->norm1.d.ptr : nullptr, xa.ptr, W, c.norm_groups, c.eps, T, f32, st),
+            "feed-forward result: gate, norm, residual"))
+      return false;
+  }
+  if (keep_trail)
+    return cu(cudaMemcpyAsync((char*)trail.ptr + (size_t)li * T * W * 4, x.ptr, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st), "trail copy");
+  return true;
+}
+
 // everything between the metadata upload and the final synchronisation: launches only (no allocation, no synchronisation)
 bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
   const int* M = meta_d.i32();
@@ -759,6 +997,12 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
     if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, W, T, c.f32, st), "embedding")) return false;
     for (int li = 0; li < c.n_layers; ++li)
       if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
+  } else if (c.block_kind == 2) {
+    if (!rc(k.pk_res32_embed_gnorm(embed.d.ptr, d_tok, embed_norm.d.ptr, (float*)x.ptr, layers[0].norm1.d.ptr, xa.ptr, W, c.norm_groups, c.eps, T, c.f32, st),
+            "embedding"))
+      return false;
+    for (int li = 0; li < c.n_layers; ++li)
+      if (!run_sandwich_layer(li, T, max_kv, M, n)) return false;
   } else {
     if (!rc(k.pk_res32_embed_scaled(embed.d.ptr, d_tok, (float*)x.ptr, W, T, c.embed_scale, c.f32, st), "embedding")) return false;
     // every layer's residual sum is folded into the next layer's norm (the last one into a plain sum)
@@ -778,13 +1022,15 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
   if (n_rows > 0) {
     if (c.block_kind == 0) {
       if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, n_rows, c.eps, c.f32, st), "final norm")) return false;
+    } else if (c.block_kind == 2) {
+      if (!rc(k.pk_res32_gnorm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, c.norm_groups, c.eps, n_rows, c.f32, st), "final norm")) return false;
     } else if (!rc(k.pk_res32_dyt_rows((const float*)x.ptr, d_rows, (const float*)final_alpha32.ptr, final_norm.d.ptr, final_b.d.ptr, xr.ptr, W, n_rows, c.f32,
                                        st),
                    "final norm")) {
       return false;
     }
     if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
-    const float ls = c.block_kind == 1 ? c.logit_scale : 1.f;
+    const float ls = c.block_kind >= 1 ? c.logit_scale : 1.f;
     if (!rc(k.pk_scale_to_f32(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, st), "logits")) return false;
     if (want_sample) {
       const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;

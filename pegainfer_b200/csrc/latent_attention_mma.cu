@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(128 * WG)
 latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict__ cache, const bf16* __restrict__ sink, const int* __restrict__ pos,
                             const int* __restrict__ req, const int* __restrict__ page_off, const int* __restrict__ pages, bf16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, long page_stride, int page_size, int tokens, int heads, int rank,
-                            int rot, float scale) {
+                            int rot, float scale, int window) {
   constexpr int ROWS_G = 16 * MT, ROWS = ROWS_G * WG, NR = 2 * MT;  // NR = rows per thread: rb + g + 8 * i, i < NR
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = rank + rot, ldk = D + 8, nv = rank / 32;
@@ -79,9 +79,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
     const int rq = req[t];
     int t_end = t;
     while (t_end + 1 <= t_last && req[t_end + 1] == rq) ++t_end;
-    const int kv_end = pos[t_end] + 1;
-    const int per = ((kv_end + nsplit - 1) / nsplit + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
-    const int k_begin = split * per, k_end = min(kv_end, k_begin + per);
+    const int kv_end = pos[t_end] + 1, kv_lo = window > 0 ? max(pos[t] - window + 1, 0) : 0;  // keys any row of this run can see
+    const int per = ((kv_end - kv_lo + nsplit - 1) / nsplit + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
+    const int k_begin = kv_lo + split * per, k_end = min(kv_end, k_begin + per);
     const int* pg = pages + page_off[rq];
     bool act[NR];
 #pragma unroll
@@ -146,7 +146,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = mt * 2 + (e >> 1), j = j0 + warp * 16 + nt * 8 + 2 * tq + (e & 1);
-            const bool vis = act[i] && j < k_end && j <= row_pos[i];
+            const bool vis = act[i] && j < k_end && j <= row_pos[i] && (window <= 0 || j > row_pos[i] - window);
             s[mt][nt][e] = vis ? s[mt][nt][e] * scale : kNegBig;
             mx[i] = fmaxf(mx[i], s[mt][nt][e]);
           }
@@ -236,10 +236,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
     const int r = rb + g + 8 * i, R = R0 + r, mt = i >> 1, hf = i & 1;
     if (R >= total_rows) continue;
     if (nsplit == 1) {
-      const float sk = bf2f(sink[R % heads]);
+      const float sk = sink ? bf2f(sink[R % heads]) : kNegBig;
       const float M = fmaxf(m_run[i], sk);
       const float w = __expf(m_run[i] - M);
-      const float inv = w / (l_run[i] * w + __expf(sk - M));
+      const float inv = w / (l_run[i] * w + (sink ? __expf(sk - M) : 0.f));
 #pragma unroll
       for (int n = 0; n < NV; ++n)
         if (n < nv)
@@ -266,7 +266,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
   const int R = blockIdx.x, tile = R / tile_rows, r = R % tile_rows;
   const size_t slot0 = (size_t)tile * nsplit * tile_rows + r;  // split s at slot0 + s * tile_rows
   if (threadIdx.x < 32) {
-    const float sk = bf2f(sink[R % heads]);
+    const float sk = sink ? bf2f(sink[R % heads]) : kNegBig;
     float m[2], l[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -276,7 +276,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     }
     const float M = fmaxf(warp_max(fmaxf(m[0], m[1])), sk);
     const float e0 = __expf(m[0] - M), e1 = __expf(m[1] - M);
-    const float inv = 1.f / (warp_sum(l[0] * e0 + l[1] * e1) + __expf(sk - M));
+    const float inv = 1.f / (warp_sum(l[0] * e0 + l[1] * e1) + (sink ? __expf(sk - M) : 0.f));
     wgt[threadIdx.x] = e0 * inv;
     wgt[threadIdx.x + 32] = e1 * inv;
   }
@@ -300,14 +300,14 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
 template <int NV, int MT, int WG>
 static cudaError_t launch_mma(dim3 grid, size_t smem, cudaStream_t st, const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req,
                               const int* page_off, const int* pages, bf16* out, float* po, float* pml, long page_stride, int page_size, int tokens,
-                              int heads, int rank, int rot, float scale) {
+                              int heads, int rank, int rot, float scale, int window) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(latent_attention_mma_kernel<NV, MT, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_done = true;
   }
   return launch(latent_attention_mma_kernel<NV, MT, WG>, grid, dim3(128 * WG), smem, st, true, qa, cache, sink, pos, req, page_off, pages, out, po, pml,
-                page_stride, page_size, tokens, heads, rank, rot, scale);
+                page_stride, page_size, tokens, heads, rank, rot, scale, window);
 }
 
 static size_t mma_smem_bytes(int rows, int D) { return (size_t)(rows + 2 * kMmaKeys) * (D + 8) * 2 + (size_t)rows * 72 * 2 + (size_t)8 * rows * 4; }
@@ -315,8 +315,9 @@ static size_t mma_smem_bytes(int rows, int D) { return (size_t)(rows + 2 * kMmaK
 // 0 = launched; -2 = shape / alignment outside this kernel (the caller runs the generic kernel)
 int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off,
                                 const int* pages, bf16* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
-                                int max_kv_len, cudaStream_t st) {
+                                int window, int max_kv_len, cudaStream_t st) {
   const int D = rank + rot;
+  if (window > 0) max_kv_len = min(max_kv_len, window + tokens);  // no row sees more keys than that
   if (rank % 64 || rot % 16 || rank > 512 || page_stride % 8 || (reinterpret_cast<uintptr_t>(qa) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 3))
     return -2;
@@ -339,7 +340,7 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
   const int nv = rank / 32;
   cudaError_t e;
 #define PK_LAUNCH_MMA(NVV, WGG) \
-  launch_mma<NVV, 1, WGG>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale)
+  launch_mma<NVV, 1, WGG>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale, window)
   if (wg == 2) {
     if (nv <= 2) e = PK_LAUNCH_MMA(2, 2);
     else if (nv <= 4) e = PK_LAUNCH_MMA(4, 2);

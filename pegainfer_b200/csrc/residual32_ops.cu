@@ -5,6 +5,8 @@
 // the latent attention in either type).  Every kernel is templated on the activation / weight element type E
 // (bf16 or float); arithmetic is fp32 throughout and a value is rounded once, when it is stored as E.
 // All of these are HBM-bound except the GEMM: 4 - 12 bytes per element per pass.
+#include <algorithm>
+
 #include "common.cuh"
 #include "typed.cuh"
 
@@ -255,6 +257,120 @@ __global__ void scale_to_f32_kernel(const A* __restrict__ in, float* __restrict_
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = to_f(in[i]) * scale;
 }
 
+
+// ---- RMS norm in groups and "sandwich" blocks (a norm before AND after each sublayer):
+//   gnorm(v, w)[i] = v[i] / sqrt(mean_{k in group(i)} v[k]^2 + eps) * w[i],  a row is `groups` equal consecutive parts.
+//   x <- x + mult * gnorm((y + bias) * logistic(gate + gate_bias), w_post);   h = gnorm(x, w_next)
+// One CTA per token; the row lives in shared memory as fp32, statistics and the residual sum are fp32.
+
+// reciprocal root mean square of every group of row[0 .. width): each group is summed by `parts` warps over fixed slices and
+// the slices are added in order, so the result does not depend on timing.  part_s: >= max(groups, warps) floats, inv_s: groups.
+__device__ __forceinline__ void group_inv_rms(const float* row, int width, int groups, float eps, float* part_s, float* inv_s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int gsz = width / groups, parts = nw > groups ? nw / groups : 1, items = groups * parts, slice = (gsz + parts - 1) / parts;
+  __syncthreads();  // the row is complete (and nobody still reads the previous statistics)
+  for (int it = warp; it < items; it += nw) {
+    const int g = it / parts, pt = it % parts;
+    const int lo = pt * slice, hi = min(gsz, lo + slice);
+    float ss = 0.f;
+    for (int i = lo + lane; i < hi; i += 32) {
+      const float v = row[g * gsz + i];
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) part_s[it] = ss;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float ss = 0.f;
+    for (int pt = 0; pt < parts; ++pt) ss += part_s[g * parts + pt];
+    inv_s[g] = 1.f / sqrtf(ss / (float)gsz + eps);
+  }
+  __syncthreads();
+}
+
+// x[t] = gnorm(embed[ids[t]], w_embed);  h[t] = gnorm(x[t], w_next) in the element type (w_next may be null)
+template <typename E>
+__global__ void embed_gnorm_kernel(const E* __restrict__ embed, const int* __restrict__ tok, const E* __restrict__ w_embed, float* __restrict__ x,
+                                   const E* __restrict__ w_next, E* __restrict__ h, int width, int groups, float eps) {
+  extern __shared__ float gn_sm[];
+  float* row = gn_sm;
+  float* inv_s = row + width;
+  float* part_s = inv_s + groups;
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, gsz = width / groups;
+  const E* src = embed + (size_t)tok[t] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = to_f(src[i]);
+  group_inv_rms(row, width, groups, eps, part_s, inv_s);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float r = row[i] * inv_s[i / gsz] * to_f(w_embed[i]);
+    x[(size_t)t * width + i] = r;
+    row[i] = r;
+  }
+  if (!w_next) return;
+  group_inv_rms(row, width, groups, eps, part_s, inv_s);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h[(size_t)t * width + i] = from_f<E>(row[i] * inv_s[i / gsz] * to_f(w_next[i]));
+}
+
+// The step between two sublayers of a sandwich block.  y [tokens, width] (E or float) is a sublayer's result, `bias` (may be null)
+// its projection bias, `gate` (may be null; rows of stride gate_ld, + gate_bias) the pre-activation of its logistic gate.
+template <typename E, typename Y>
+__global__ void gated_gnorm_add_kernel(const Y* __restrict__ y, const E* __restrict__ bias, const E* __restrict__ gate, long gate_ld,
+                                       const E* __restrict__ gate_bias, const E* __restrict__ w_post, float mult, float* __restrict__ x,
+                                       const E* __restrict__ w_next, E* __restrict__ h, int width, int groups, float eps) {
+  extern __shared__ float gn_sm[];
+  float* row = gn_sm;
+  float* inv_s = row + width;
+  float* part_s = inv_s + groups;
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, gsz = width / groups;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = to_f(y[(size_t)t * width + i]) + (bias ? to_f(bias[i]) : 0.f);
+    if (gate) {
+      const float z = to_f(gate[(size_t)t * gate_ld + i]) + (gate_bias ? to_f(gate_bias[i]) : 0.f);
+      v *= 1.f / (1.f + expf(-z));
+    }
+    row[i] = v;
+  }
+  group_inv_rms(row, width, groups, eps, part_s, inv_s);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float r = x[(size_t)t * width + i] + mult * (row[i] * inv_s[i / gsz] * to_f(w_post[i]));
+    x[(size_t)t * width + i] = r;
+    row[i] = r;
+  }
+  if (!w_next) return;
+  group_inv_rms(row, width, groups, eps, part_s, inv_s);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h[(size_t)t * width + i] = from_f<E>(row[i] * inv_s[i / gsz] * to_f(w_next[i]));
+}
+
+// out[r] = gnorm(x[rows[r]], w) in the element type: the model's last norm, only for the rows whose logits are wanted
+template <typename E>
+__global__ void gnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const E* __restrict__ w, E* __restrict__ out, int width,
+                                  int groups, float eps) {
+  extern __shared__ float gn_sm[];
+  float* row = gn_sm;
+  float* inv_s = row + width;
+  float* part_s = inv_s + groups;
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const float* xr = x + (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * width;
+  const int gsz = width / groups;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = xr[i];
+  group_inv_rms(row, width, groups, eps, part_s, inv_s);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)blockIdx.x * width + i] = from_f<E>(row[i] * inv_s[i / gsz] * to_f(w[i]));
+}
+
+constexpr int kGnormThreads = 256;
+static inline size_t gnorm_smem(int width, int groups) { return (size_t)(width + groups + std::max(groups, kGnormThreads / 32)) * sizeof(float); }
+template <typename K>
+static bool gnorm_fits(K kernel, size_t smem) {  // rows above 48 KB of shared memory need the opt-in limit (set once per kernel)
+  if (smem <= 48 * 1024) return true;
+  if (smem > 200 * 1024) return false;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -382,5 +498,50 @@ extern "C" int pk_scale_to_f32(const void* in, int in_f32, float* out, long n, f
   const dim3 g(grid_1d(n, 256)), b(256);
   if (in_f32) launch(scale_to_f32_kernel<float>, g, b, 0, st, true, (const float*)in, out, n, scale);
   else launch(scale_to_f32_kernel<bf16>, g, b, 0, st, true, (const bf16*)in, out, n, scale);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_embed_gnorm(const void* embed, const int* token_ids, const void* w_embed, float* x, const void* w_next, void* h, int width,
+                                    int groups, float eps, int tokens, int f32, pk_stream st) {
+  if (!embed || !token_ids || !w_embed || !x || (w_next && !h) || width <= 0 || groups <= 0 || width % groups || tokens <= 0) return -1;
+  const size_t sm = gnorm_smem(width, groups);
+  if (!(f32 ? gnorm_fits(embed_gnorm_kernel<float>, sm) : gnorm_fits(embed_gnorm_kernel<bf16>, sm))) return -2;
+  PK_BY_TYPE(f32,
+             launch(embed_gnorm_kernel<float>, dim3(tokens), dim3(kGnormThreads), sm, st, true, (const float*)embed, token_ids, (const float*)w_embed, x,
+                    (const float*)w_next, (float*)h, width, groups, eps),
+             launch(embed_gnorm_kernel<bf16>, dim3(tokens), dim3(kGnormThreads), sm, st, true, (const bf16*)embed, token_ids, (const bf16*)w_embed, x,
+                    (const bf16*)w_next, (bf16*)h, width, groups, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_gated_gnorm_add(const void* y, int y_is_f32, const void* bias, const void* gate, long gate_ld, const void* gate_bias,
+                                        const void* w_post, float mult, float* x, const void* w_next, void* h, int width, int groups, float eps,
+                                        int tokens, int f32, pk_stream st) {
+  if (!y || !w_post || !x || (w_next && !h) || width <= 0 || groups <= 0 || width % groups || tokens <= 0) return -1;
+  const size_t sm = gnorm_smem(width, groups);
+  const dim3 g(tokens), b(kGnormThreads);
+  if (f32) {
+    if (!gnorm_fits(gated_gnorm_add_kernel<float, float>, sm)) return -2;
+    launch(gated_gnorm_add_kernel<float, float>, g, b, sm, st, true, (const float*)y, (const float*)bias, (const float*)gate, gate_ld,
+           (const float*)gate_bias, (const float*)w_post, mult, x, (const float*)w_next, (float*)h, width, groups, eps);
+  } else if (y_is_f32) {
+    if (!gnorm_fits(gated_gnorm_add_kernel<bf16, float>, sm)) return -2;
+    launch(gated_gnorm_add_kernel<bf16, float>, g, b, sm, st, true, (const float*)y, (const bf16*)bias, (const bf16*)gate, gate_ld,
+           (const bf16*)gate_bias, (const bf16*)w_post, mult, x, (const bf16*)w_next, (bf16*)h, width, groups, eps);
+  } else {
+    if (!gnorm_fits(gated_gnorm_add_kernel<bf16, bf16>, sm)) return -2;
+    launch(gated_gnorm_add_kernel<bf16, bf16>, g, b, sm, st, true, (const bf16*)y, (const bf16*)bias, (const bf16*)gate, gate_ld,
+           (const bf16*)gate_bias, (const bf16*)w_post, mult, x, (const bf16*)w_next, (bf16*)h, width, groups, eps);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_gnorm_rows(const float* x, const int* rows, const void* w, void* out, int width, int groups, float eps, int n_rows, int f32,
+                                   pk_stream st) {
+  if (!x || !w || !out || width <= 0 || groups <= 0 || width % groups || n_rows <= 0) return -1;
+  const size_t sm = gnorm_smem(width, groups);
+  if (!(f32 ? gnorm_fits(gnorm_rows_kernel<float>, sm) : gnorm_fits(gnorm_rows_kernel<bf16>, sm))) return -2;
+  PK_BY_TYPE(f32, launch(gnorm_rows_kernel<float>, dim3(n_rows), dim3(kGnormThreads), sm, st, true, x, rows, (const float*)w, (float*)out, width, groups, eps),
+             launch(gnorm_rows_kernel<bf16>, dim3(n_rows), dim3(kGnormThreads), sm, st, true, x, rows, (const bf16*)w, (bf16*)out, width, groups, eps));
   return (int)cudaGetLastError();
 }

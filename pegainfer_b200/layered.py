@@ -23,13 +23,15 @@ class LayerCfg(C.Structure):
                [(n, C.c_int) for n in ("mlp_kind", "ff", "experts", "top", "groups", "keep")] + \
                [("route_scale", C.c_float), ("expert_ff", C.c_int), ("shared_ff", C.c_int)] + \
                [(n, C.c_int) for n in ("mixer_kind", "kv_heads", "chunk", "conv", "rot_interleaved")] + [("gate_cap", C.c_float)] + \
-               [(n, C.c_int) for n in ("router_kind", "expert_act")]
+               [(n, C.c_int) for n in ("router_kind", "expert_act", "window")] + [("softcap", C.c_float), ("slope_log2", C.c_float)] + \
+               [(n, C.c_int) for n in ("value_norm", "sink_kind", "out_gate", "proj_bias")]
 
 
 class ModelCfg(C.Structure):
     _fields_ = [("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("eps", C.c_float)] + \
                [(n, C.c_int) for n in ("f32", "page_size", "num_pages", "max_requests", "device", "enable_pdl", "block_kind")] + \
-               [("embed_scale", C.c_float), ("logit_scale", C.c_float)]
+               [("embed_scale", C.c_float), ("logit_scale", C.c_float), ("norm_groups", C.c_int), ("residual_mult", C.c_float),
+                ("gated_residual", C.c_int)]
 
 
 def typed_host():
@@ -105,7 +107,8 @@ class LayeredModel:
             lcs[i] = self.layer_struct(l)
         mc = self.model_struct(cfg, ModelCfg(vocab=cfg.vocab, width=cfg.width, n_layers=len(cfg.layers), eps=cfg.eps, f32=f32, page_size=PAGE_SIZE,
                                              num_pages=pages_for(max_tokens) if max_tokens > 0 else 0, max_requests=max_requests, device=device_ordinal,
-                                             enable_pdl=int(enable_pdl), block_kind=0, embed_scale=1.0, logit_scale=1.0))
+                                             enable_pdl=int(enable_pdl), block_kind=0, embed_scale=1.0, logit_scale=1.0, norm_groups=1,
+                                             residual_mult=1.0, gated_residual=0))
         torch.cuda.set_device(device_ordinal)
         self._m = self._h.pv_create(C.byref(mc), lcs, (kernel_lib or ffi.KERNEL_LIB_PATH).encode())
         if not self._m:

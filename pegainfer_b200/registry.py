@@ -23,6 +23,11 @@ def _load_risolorn(path, dtype, max_tokens, max_requests, **kw):
     return RisolornModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
 
 
+def _load_nagosun(path, dtype, max_tokens, max_requests, **kw):
+    from .nagosun import NagosunModel
+    return NagosunModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
+
+
 def _load_qwen3(path, dtype, max_tokens, max_requests, **kw):
     from .config import PAGE_SIZE
     from .model import ModelRuntimeConfig, Qwen3Model
@@ -36,11 +41,12 @@ def _load_qwen3(path, dtype, max_tokens, max_requests, **kw):
 ARCHITECTURES = {
     "Vamadra": _load_vamadra,
     "Risolorn": _load_risolorn,
+    "Nagosun": _load_nagosun,
     "Qwen3ForCausalLM": _load_qwen3,
     "qwen3": _load_qwen3,
 }
 # designs whose kernels run with every product in fp32 as well
-FLOAT32_CAPABLE = {"Vamadra", "Risolorn"}
+FLOAT32_CAPABLE = {"Vamadra", "Risolorn", "Nagosun"}
 
 
 def architecture_of(model_path: str) -> str:
