@@ -545,6 +545,8 @@ typedef struct pk_attn_extra {
 int pk_gqa_attention_ex(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                         const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim, int vdim,
                         float scale, int chunk, const pk_attn_extra* extra, int f32, pk_stream st);
+/* out[r] = arg-max of logits[r, :vocab] (fp32 rows; lowest index on ties) */
+int pk_top1_rows_f32(const float* logits, int* out, int rows, int vocab, pk_stream stream);
 /* pk_rope_slice / pk_latent_kv_append with a choice of pairing: interleaved 1 rotates (2i, 2i + 1), 0 rotates (i, i + dims/2) */
 int pk_rope_slice_ex(const void* in, void* out, const int* positions, const float* freq, float mag, int tokens, int heads, int in_stride, int in_off,
                      int out_stride, int out_off, int width, int dims, int interleaved, int f32, pk_stream st);

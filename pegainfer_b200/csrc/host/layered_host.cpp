@@ -84,7 +84,7 @@ struct Lib {
 #define PV_COMMON(X)                                                                                                                       \
   X(cuda_set_device) X(cublas_init) X(cublas_destroy) X(gemm_cuda) X(flashinfer_top1_cuda) X(pk_b200_set_pdl) X(pk_b200_launch_count)      \
   X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_proj_rows_f32out) \
-  X(pk_scale_to_f32) X(pk_moe_up_act) X(pk_moe_grouped_act)
+  X(pk_scale_to_f32) X(pk_moe_up_act) X(pk_moe_grouped_act) X(pk_top1_rows_f32)
 #define PV_BLOCK0(X)                                                                                                                        \
   X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_act) X(pk_rope_slice) X(pk_latent_kv_append)             \
   X(pk_latent_attention) X(pk_router_grouped_topk) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
@@ -1033,13 +1033,13 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
     const float ls = c.block_kind >= 1 ? c.logit_scale : 1.f;
     if (!rc(k.pk_scale_to_f32(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, st), "logits")) return false;
     if (want_sample) {
-      const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
-      if (c.f32 || ls != 1.f) {  // the sampler reads bf16 rows of the final (scaled) logits
-        if (!rc(k.pk_convert(logits_f.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
-        lb = (const pk_bf16*)logits_bf.ptr;
+      if (c.f32 || ls != 1.f) {  // the final (scaled) logits exist in fp32 only: greedy token of every row from those
+        if (!rc(k.pk_top1_rows_f32((const float*)logits_f.ptr, sampled_d.i32(), n_rows, c.vocab, st), "greedy token")) return false;
+      } else {
+        const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
+        for (int i = 0; i < n_rows; ++i)
+          k.flashinfer_top1_cuda(lb + (size_t)i * c.vocab, (pk_bf16*)top1_val.ptr, (uint8_t*)top1_states.ptr, sampled_d.i32() + i, c.vocab, st);
       }
-      for (int i = 0; i < n_rows; ++i)
-        k.flashinfer_top1_cuda(lb + (size_t)i * c.vocab, (pk_bf16*)top1_val.ptr, (uint8_t*)top1_states.ptr, sampled_d.i32() + i, c.vocab, st);
       if (!cu(cudaMemcpyAsync(sampled_h, sampled_d.ptr, (size_t)std::min(n_rows, 1024) * 4, cudaMemcpyDeviceToHost, st), "sampled tokens")) return false;
     }
   }

@@ -180,7 +180,7 @@ extern "C" int pk_rope_slice(const void* in, void* out, const int* positions, co
 
 extern "C" int pk_rope_slice_ex(const void* in, void* out, const int* positions, const float* freq, float mag, int tokens, int heads, int in_stride,
                                 int in_off, int out_stride, int out_off, int width, int dims, int interleaved, int f32, pk_stream st) {
-  if (!in || !out || !positions || !freq || tokens <= 0 || heads <= 0 || width <= 0 || dims < 0 || dims > width || (dims & 1)) return -1;
+  if (!in || !out || !positions || (dims > 0 && !freq) || tokens <= 0 || heads <= 0 || width <= 0 || dims < 0 || dims > width || (dims & 1)) return -1;
   const dim3 rope_grid(tokens, tokens >= 64 ? 1 : (heads * width + 127) / 128);  // few tokens: spread one token over CTAs
   if (f32)
     launch(rope_slice_kernel<float>, rope_grid, dim3(128), 0, st, true, (const float*)in, (float*)out, positions, freq, mag, heads, in_stride,
@@ -201,8 +201,8 @@ extern "C" int pk_latent_kv_append(const void* dkv, const void* norm_w, const in
 extern "C" int pk_latent_kv_append_ex(const void* dkv, const void* norm_w, const int* positions, const int* req, const int* page_off, const int* pages,
                                       void* cache, long page_stride, int page_size, int rank, int rot, int dims, int interleaved, const float* freq,
                                       float mag, float eps, int tokens, int f32, pk_stream st) {
-  if (!dkv || !norm_w || !positions || !req || !page_off || !pages || !cache || !freq || tokens <= 0 || rank <= 0 || rot < 0 || dims > rot ||
-      (dims & 1) || page_size <= 0)
+  if (!dkv || !norm_w || !positions || !req || !page_off || !pages || !cache || (dims > 0 && !freq) || tokens <= 0 || rank <= 0 || rot < 0 || dims < 0 ||
+      dims > rot || (dims & 1) || page_size <= 0)
     return -1;
   if (f32)
     launch(latent_kv_append_kernel<float>, dim3(tokens), dim3(128), 0, st, true, (const float*)dkv, (const float*)norm_w, positions, req, page_off,

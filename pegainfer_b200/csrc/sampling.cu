@@ -148,6 +148,62 @@ void flashinfer_top1_cuda(const pk_bf16* logits, pk_bf16* top1_value_scratch,
 
 }  // extern "C"
 
+// Greedy token of fp32 logits rows (models whose logits leave the head in fp32, e.g. with an output multiplier): one CTA per
+// row, highest value, lowest index on ties.
+namespace pk {
+__global__ void top1_rows_f32_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_wait();
+  const float* x = logits + (size_t)blockIdx.x * vocab;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = x[i];
+    if (v > bv || (v == bv && i < bi)) {
+      bv = v;
+      bi = i;
+    }
+  }
+  auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) {
+    sv[w] = bv;
+    si[w] = bi;
+  }
+  __syncthreads();
+  if (w == 0) {
+    bv = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, bv, bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+}  // namespace pk
+
+extern "C" int pk_top1_rows_f32(const float* logits, int* out, int rows, int vocab, pk_stream stream) {
+  if (!logits || !out || rows <= 0 || vocab <= 0) return -1;
+  pk::launch(pk::top1_rows_f32_kernel, dim3(rows), dim3(vocab >= 4096 ? 1024 : 256), 0, stream, true, logits, out, vocab);
+  return (int)cudaGetLastError();
+}
+
 // =====================================================================================================
 // Non-greedy sampling: temperature softmax + top-k / top-p filtering + multinomial draw.
 // Replaces csrc/flashinfer_sampling.cu:13-110 (logits_to_probs_kernel + FlashInfer

@@ -109,6 +109,13 @@ EXT_SIGNATURES = {
 
 # fp32-residual / latent-attention / mixture-of-experts ops (element type chosen by an `f32` flag behind void pointers)
 i64l = C.c_long
+
+
+class AttnExtra(C.Structure):
+    """pk_attn_extra: options of pk_gqa_attention_ex (a zero / NULL field switches its option off)."""
+    _fields_ = [("window", i32), ("softcap", f32), ("slope_log2", f32), ("gate", vp), ("gate_ld", i64l)]
+
+
 RES32_SIGNATURES = {
     "pk_res32_embed": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "pk_res32_offset_norm_add": (i32, [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp]),
@@ -140,6 +147,16 @@ RES32_SIGNATURES = {
     "pk_router_topk_ex": (i32, [vp, i32, vp, vp, vp] + [i32] * 5 + [f32, i32, i32, i32, vp]),
     "pk_moe_up_act": (i32, [vp, vp, vp, vp] + [i32] * 6 + [vp]),
     "pk_moe_grouped_act": (i32, [vp] * 9 + [i32] * 6 + [vp]),
+    # sandwich blocks with grouped RMS norm, attention options, windowed latent attention
+    "pk_res32_embed_gnorm": (i32, [vp] * 6 + [i32, i32, f32, i32, i32, vp]),
+    "pk_res32_gated_gnorm_add": (i32, [vp, i32, vp, vp, i64l, vp, vp, f32, vp, vp, vp, i32, i32, f32, i32, i32, vp]),
+    "pk_top1_rows_f32": (i32, [vp, vp, i32, i32, vp]),
+    "pk_res32_gnorm_rows": (i32, [vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]),
+    "pk_gqa_rope_append_ex": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64l] + [i32] * 7 + [vp, f32, f32, i32, i32, vp]),
+    "pk_gqa_attention_ex": (i32, [vp] * 8 + [i64l] + [i32] * 6 + [f32, i32, C.POINTER(AttnExtra), i32, vp]),
+    "pk_rope_slice_ex": (i32, [vp, vp, vp, vp, f32] + [i32] * 10 + [vp]),
+    "pk_latent_kv_append_ex": (i32, [vp] * 7 + [i64l, i32, i32, i32, i32, i32, vp, f32, f32, i32, i32, vp]),
+    "pk_latent_attention_ex": (i32, [vp] * 8 + [i64l, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp]),
 }
 
 

@@ -1,0 +1,822 @@
+"""Nagosun on the GPU against the plain fp32 oracle (oracle/nagosun_oracle.py): mechanisms alone through the C ABI or as
+one-layer models, then the model through its own step / engine / generate entry points -- whole prompts, token-by-token
+decoding, portions down to two tokens, unequal batches, reused pages and slots, keys far back, at page borders and on both
+sides of every window's edge, the first tokens, long decoding, greedy generation.
+
+Configurations and weights are made here (small, random, seeded).  float32 runs are held to 2e-4 of the logits' spread,
+bfloat16 runs to rounding noise.  Where random weights would blur a fault (one far key among hundreds, the sink, a window's
+edge) the inputs are built so that a single score dominates.
+"""
+import ctypes as C
+import math
+import random
+
+import pytest
+import torch
+
+from oracle import nagosun_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+
+
+# ------------------------------------------------------------------ configurations (none is a real checkpoint's)
+def attn(heads, kv_heads, dim, vdim, window, cap=30.0, scale=None):
+    mx = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    if window:
+        mx["mask"] = {"size": window}
+    if cap:
+        mx["softcap"] = cap
+    return {"type": "attention", "mixer": mx}
+
+
+def latent(heads, dim, rot_dim, vdim, rank, window, rot_dims=None, base=10000.0, scale=None):
+    mx = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+          "scale": scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim), "rot": {"dims": rot_dim if rot_dims is None else rot_dims, "base": base}}
+    if window:
+        mx["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": mx}
+
+
+def model_cfg(layers, vocab=211, width=88, eps=1e-5, groups=4, mult=0.6, logit=0.5):
+    return {"architecture": "Nagosun", "vocab": vocab, "width": width, "norm": {"eps": eps, "groups": groups}, "residual_mult": mult,
+            "logit_scale": logit, "layers": [dict(l, mlp={"kind": "dense", "ff": ff} if ff else None) for l, ff in layers]}
+
+
+def cfg_general():
+    """All sizes differ from each other; both mixers; a layer without feed-forward; windows shorter than the test sequences.  In bf16
+    layer 0 takes the tensor-core attention for its prompt portions, layer 2 the generic one; the latent layers the generic one."""
+    return model_cfg([(attn(6, 2, 32, 32, 40), 56), (latent(3, 24, 8, 20, 40, 23), 0), (attn(4, 4, 24, 40, 37, cap=8.0), 48),
+                      (latent(5, 16, 16, 12, 48, 50, rot_dims=8, base=300.0), 72)])
+
+
+def cfg_edges():
+    """Values that often coincide or equal one are made to differ: one head, kv_heads == heads, a window of one token (a query sees
+    itself only) and of two, no mask at all, no soft cap, one norm group and as many groups as entries, a width that is no multiple
+    of 8, fewer rotated entries than the rotated slice is wide, a slice that does not rotate, multipliers of one."""
+    a = attn(1, 1, 12, 20, 1)
+    b = attn(3, 3, 8, 8, 0, cap=0.0)
+    c = latent(1, 12, 6, 10, 20, 2, rot_dims=4)
+    d = latent(2, 8, 4, 16, 12, 0, rot_dims=0)
+    return model_cfg([(a, 28), (c, 0), (b, 20), (d, 36)], vocab=97, width=52, eps=1e-6, groups=1, mult=1.0, logit=1.0)
+
+
+def cfg_each_entry_its_own_group():
+    """groups == width turns the norm into v / sqrt(v^2 + eps) entry by entry, which multiplies rounding differences of entries near
+    zero by 1 / sqrt(eps): a large eps keeps the comparison meaningful"""
+    return model_cfg([(attn(2, 1, 16, 8, 9), 24), (latent(2, 8, 8, 8, 16, 7), 16)], vocab=80, width=24, eps=1e-2, groups=24, mult=1.3, logit=2.0)
+
+
+def cfg_tensor_tiles():
+    """head sizes and ranks that the tensor-core kernels take in bf16 (attention: dim == vdim in {32, 64, 96, 128}; latent: rank a
+    multiple of 64, rotated slice a multiple of 16); windows of a whole number of pages, and not"""
+    return model_cfg([(attn(4, 1, 64, 64, 64), 64), (latent(4, 32, 16, 32, 64, 48), 0), (attn(2, 2, 128, 128, 70, cap=15.0), 96),
+                      (latent(3, 24, 32, 40, 128, 100), 64), (attn(3, 1, 96, 96, 33), 0)], vocab=128, width=64, groups=2)
+
+
+CONFIGS = {"general": cfg_general, "edges": cfg_edges, "groups": cfg_each_entry_its_own_group, "tiles": cfg_tensor_tiles}
+SHARP = {F32: 5.0, BF16: 2.0}
+
+
+def sharp_for(name, dtype):
+    """one-entry groups already multiply rounding differences; sharpened (large) scores on top would drown the comparison, and so
+    does bfloat16 rounding (that combination is covered at kernel level, where the inputs are the same on both sides)"""
+    if name == "groups" and dtype == BF16:
+        pytest.skip("v / sqrt(v^2 + eps) per entry multiplies bf16 rounding of entries near zero by 1 / sqrt(eps)")
+    return 1.0 if name == "groups" else SHARP[dtype]
+
+
+def make_weights(cfg, seed, sharp=1.0):
+    """bf16 checkpoint; `sharp` scales the query projections so that the softmax is peaked on single keys."""
+    from pegainfer_b200.nagosun import NagosunConfig, weight_shapes
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in weight_shapes(NagosunConfig.from_dict(cfg)).items():
+        leaf = name.rsplit(".", 1)[-1]
+        rn = lambda s=1.0: s * torch.randn(shape, generator=g)  # noqa: E731
+        if leaf.startswith("norm"):
+            t = 1.0 + 0.2 * rn()
+        elif len(shape) == 1:
+            t = rn(0.4)
+        elif name == "embed":
+            t = rn()
+        else:
+            t = rn() / math.sqrt(shape[1])
+            if name.endswith("mix.q"):
+                t = t * sharp
+        w[name] = t.to(BF16)
+    return w
+
+
+def build(cfg, w, dtype, max_tokens=1024, max_requests=4):
+    from pegainfer_b200.nagosun import NagosunConfig, NagosunModel
+    return NagosunModel(NagosunConfig.from_dict(cfg), w, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests)
+
+
+def row_errors(got, want):
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
+
+
+def close(got, want, dtype):
+    """float32: every row within 2e-4 of the logits' spread.  bfloat16: rounding noise only -- half of the rows within 4 %, 85 in 100
+    within 10 % (a wrong key, window, page or slot shows in the float32 run of the same test)."""
+    e = row_errors(got, want)
+    if dtype == F32:
+        return e.max().item() < 2e-4
+    return e.median().item() < 0.04 and e.quantile(0.85).item() < 0.10
+
+
+def tokens_for(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def oracle_logits(cfg, w, toks, trail=None):
+    """the oracle in float64: its own rounding then stays far below what a float32 run is held to"""
+    t64 = [] if trail is not None else None
+    out = O.forward(cfg, w, toks, t64, dtype=torch.float64).to(F32)
+    if trail is not None:
+        trail.extend(x.to(F32) for x in t64)
+    return out
+
+
+# ------------------------------------------------------------------ kernels alone
+@pytest.fixture(scope="module")
+def lib():
+    from pegainfer_b200 import ffi
+    ffi.lib().cublas_init()
+    return ffi.lib()
+
+
+def dev(t, dtype):
+    return t.to(dtype).cuda().contiguous()
+
+
+def i32(xs):
+    return torch.tensor(xs, dtype=torch.int32, device="cuda")
+
+
+class Hold:
+    """ptr(t) returns t's device address and keeps t alive until the launches that read it are done."""
+
+    def __init__(self):
+        self.kept = []
+
+    def __call__(self, t):
+        self.kept.append(t)
+        return t.data_ptr()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("W,groups", [(52, 1), (88, 4), (24, 24), (96, 3), (20000, 8)])
+def test_grouped_norm_between_sublayers(lib, dtype, W, groups):
+    """bias + logistic gate + norm of the result + scaled residual sum + the next sublayer's norm in one launch, against the oracle's
+    steps; then without gate / bias / next norm; rows wider than 48 KB of shared memory too"""
+    P = Hold()
+    T, eps, mult, ld = 5, 1e-5, 0.8, W + 16
+    g = torch.Generator().manual_seed(1)
+    rn = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    x, y, gate = rn(T, W), rn(T, W).to(dtype).to(F32), rn(T, ld).to(dtype).to(F32)
+    bias, gbias = (0.3 * rn(W)).to(dtype).to(F32), (0.3 * rn(W)).to(dtype).to(F32)
+    wp, wn = (1 + 0.3 * rn(W)).to(dtype).to(F32), (1 + 0.3 * rn(W)).to(dtype).to(F32)
+    f32 = int(dtype == F32)
+    tol = 2e-5 if dtype == F32 else 2e-2
+    for use_gate, use_bias, use_next in [(True, True, True), (False, False, True), (True, False, False)]:
+        xd, h = x.cuda(), torch.zeros(T, W, dtype=dtype, device="cuda")
+        gd = dev(gate, dtype)
+        rc = lib.pk_res32_gated_gnorm_add(P(dev(y, dtype)), f32, P(dev(bias, dtype)) if use_bias else None, gd.data_ptr() + 8 * gd.element_size() if use_gate else None,
+                                          ld, P(dev(gbias, dtype)) if use_gate else None, P(dev(wp, dtype)), mult, xd.data_ptr(),
+                                          P(dev(wn, dtype)) if use_next else None, h.data_ptr(), W, groups, eps, T, f32, None)
+        torch.cuda.synchronize()
+        assert rc == 0
+        v = y + (bias if use_bias else 0.0)
+        if use_gate:
+            v = v * torch.sigmoid(gate[:, 8:8 + W] + gbias)
+        want_x = x + mult * O.group_norm(v, wp, groups, eps)
+        assert torch.allclose(xd.cpu(), want_x, atol=1e-5, rtol=1e-5)
+        if use_next:
+            assert torch.allclose(h.float().cpu(), O.group_norm(want_x, wn, groups, eps), atol=tol, rtol=tol)
+        else:
+            assert (h == 0).all()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embedding_norm_and_last_norm(lib, dtype):
+    P = Hold()
+    V, W, groups, eps = 30, 36, 3, 1e-6
+    g = torch.Generator().manual_seed(2)
+    emb = torch.randn(V, W, generator=g).to(dtype).to(F32)
+    we, wn = (1 + 0.3 * torch.randn(W, generator=g)).to(dtype).to(F32), (1 + 0.3 * torch.randn(W, generator=g)).to(dtype).to(F32)
+    toks = [3, 29, 0, 3, 17]
+    x, h = torch.zeros(5, W, device="cuda"), torch.zeros(5, W, dtype=dtype, device="cuda")
+    f32 = int(dtype == F32)
+    assert lib.pk_res32_embed_gnorm(P(dev(emb, dtype)), P(i32(toks)), P(dev(we, dtype)), x.data_ptr(), P(dev(wn, dtype)), h.data_ptr(), W, groups, eps, 5, f32,
+                                    None) == 0
+    rows = [4, 0, 2]
+    out = torch.zeros(3, W, dtype=dtype, device="cuda")
+    assert lib.pk_res32_gnorm_rows(x.data_ptr(), P(i32(rows)), P(dev(wn, dtype)), out.data_ptr(), W, groups, eps, 3, f32, None) == 0
+    torch.cuda.synchronize()
+    want_x = O.group_norm(emb[torch.tensor(toks)], we, groups, eps)
+    tol = 2e-5 if dtype == F32 else 2e-2
+    assert torch.allclose(x.cpu(), want_x, atol=1e-5)
+    assert torch.allclose(h.float().cpu(), O.group_norm(want_x, wn, groups, eps), atol=tol, rtol=tol)
+    assert torch.allclose(out.float().cpu(), O.group_norm(want_x, wn, groups, eps)[torch.tensor(rows)], atol=tol, rtol=tol)
+
+
+def paged(req_lens, page_size, shuffle_seed=0):
+    """A page table with pages handed out in a scrambled order: (pages flat, page_off per request, number of pages)."""
+    need = [(n + page_size - 1) // page_size for n in req_lens]
+    order = torch.randperm(sum(need) + 3, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    pages, off, k = [], [], 0
+    for n in need:
+        off.append(len(pages))
+        pages += order[k:k + n]
+        k += n
+    return pages, off, sum(need) + 3
+
+
+EPS = 1e-5
+
+
+def run_attention(lib, dtype, mx, rows, bias, starts, lens, ps=16, gated=True):
+    """Bias + value norm + cache append + attention for a step whose request r brings positions starts[r] .. lens[r] - 1 (earlier
+    positions were appended by a first call from rows of the same tensor).  rows: per request [len, nq + nk + nv + ng], the
+    stacked projection outputs with the output gate's pre-activations last.  Returns [T, H * vdim]."""
+    from pegainfer_b200.ffi import AttnExtra
+    P = Hold()
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    n_qkv, ld = H * D + G * D + G * Dv, rows[0].shape[1]
+    pages, off, n_pages = paged(lens, ps, shuffle_seed=5)
+    stride = ps * G * (D + Dv) + 24
+    cache = torch.zeros(n_pages, stride, dtype=dtype, device="cuda")
+    zero_sink = torch.zeros(H, dtype=dtype, device="cuda")
+    f32 = int(dtype == F32)
+
+    def step(rows_of):  # rows_of[r] = (first position, one past the last)
+        x = torch.cat([rows[r][a:b] for r, (a, b) in enumerate(rows_of)])
+        p = [q for a, b in rows_of for q in range(a, b)]
+        rq = [r for r, (a, b) in enumerate(rows_of) for _ in range(a, b)]
+        T = len(p)
+        if T == 0:
+            return None
+        xd = dev(x, dtype)
+        qo, out = torch.zeros(T, H * D, dtype=dtype, device="cuda"), torch.zeros(T, H * Dv, dtype=dtype, device="cuda")
+        a = (P(i32(p)), P(i32(rq)), P(i32(off)), P(i32(pages)))
+        assert lib.pk_gqa_rope_append_ex(xd.data_ptr(), ld, P(dev(bias, dtype)), *a, qo.data_ptr(), cache.data_ptr(), stride, ps, H, G, D, Dv, 0, 1, None, 1.0,
+                                         EPS, T, f32, None) == 0
+        ex = AttnExtra(window=int((mx.get("mask") or {}).get("size", 0)), softcap=float(mx.get("softcap") or 0.0), slope_log2=O.SLOPE_LOG2,
+                       gate=xd.data_ptr() + n_qkv * xd.element_size() if gated else None, gate_ld=ld)
+        assert lib.pk_gqa_attention_ex(qo.data_ptr(), cache.data_ptr(), zero_sink.data_ptr(), *a, out.data_ptr(), stride, ps, T, H, G, D, Dv,
+                                       float(mx["scale"]), 0, C.byref(ex), f32, None) == 0
+        torch.cuda.synchronize()
+        return out.float().cpu()
+
+    step([(0, s) for s in starts])
+    return step([(s, n) for s, n in zip(starts, lens)])
+
+
+def oracle_attention(mx, rows, bias, lo, hi, gated=True):
+    """The oracle's attention mixer with identity projections: its input `h` IS the stacked projection output."""
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    nq, nk, nv = H * D, G * D, G * Dv
+    eye = torch.eye(rows.shape[1])
+    w = {"q": eye[:nq], "k": eye[nq:nq + nk], "v": eye[nq + nk:nq + nk + nv], "q.b": bias[:nq], "k.b": bias[nq:nq + nk], "v.b": bias[nq + nk:],
+         "g": eye[nq + nk + nv:] if gated else torch.zeros(H * Dv, rows.shape[1]), "o": torch.eye(H * Dv), "o.b": torch.zeros(H * Dv)}
+    out = O.attention_mixer(rows[:hi], w, "", mx, torch.arange(hi), EPS)[lo:]
+    return out if gated else 2.0 * out  # logistic(0) = 1/2
+
+
+# (heads, kv heads, dim, vdim, window, cap): bf16 prompts with dim == vdim in {32, 64, 96, 128} run on the tensor cores
+ATTN_SHAPES = [(3, 1, 20, 12, 50, 9.0), (6, 2, 32, 32, 48, 30.0), (4, 4, 64, 64, 100, 0.0), (2, 1, 128, 128, 64, 12.0), (5, 5, 40, 72, 33, 20.0),
+               (2, 1, 96, 96, 17, 25.0), (2, 1, 200, 136, 0, 40.0), (1, 1, 256, 256, 40, 6.0)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,D,Dv,window,cap", ATTN_SHAPES)
+def test_attention_ragged_batch(lib, dtype, H, G, D, Dv, window, cap):
+    """three requests in one launch: a 70-token portion that starts at position 90 (its first rows still see keys of the earlier
+    portion through the window), one decoded token at position 199, and the first 5 tokens of a sequence"""
+    mx = attn(H, G, D, Dv, window, cap=cap)["mixer"]
+    g = torch.Generator().manual_seed(3)
+    lens, starts = [160, 200, 5], [90, 199, 0]
+    n_all = H * D + G * D + G * Dv + H * Dv
+    rows = [torch.randn(n, n_all, generator=g).to(dtype).to(F32) for n in lens]
+    for x in rows:
+        x[:, :H * D] *= 3.0
+    bias = (0.3 * torch.randn(H * D + G * D + G * Dv, generator=g)).to(dtype).to(F32)
+    got = run_attention(lib, dtype, mx, rows, bias, starts, lens)
+    want = torch.cat([oracle_attention(mx, rows[r], bias, starts[r], lens[r]) for r in range(3)])
+    tol = 3e-5 if dtype == F32 else 4e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("prompt", [False, True])
+@pytest.mark.parametrize("window", [300, 64, 5])
+def test_attention_single_keys_at_the_windows_edges(lib, dtype, prompt, window):
+    """The last head (the flattest distance bias) aims at one key with a steep score, so its output must be that key's unit-RMS value:
+    the oldest key the window still holds, keys on both sides of page borders, the query's own position, the first tokens of a
+    sequence.  The key just behind the window, and the one just after the query, are hidden: the output must then NOT be their
+    value (and equal the oracle's, as in every case).  `prompt`: the queries sit in a 40-token portion (bf16: tensor-core kernel),
+    else they are decoded tokens."""
+    H, D = 2, 32
+    mx = attn(H, 1, D, D, window, cap=45.0, scale=1.0)["mixer"]
+    n = 700
+    g = torch.Generator().manual_seed(4)
+    val = torch.randn(n, D, generator=g).to(dtype).to(F32)
+    key = torch.nn.functional.normalize(torch.randn(n, D, generator=g), dim=-1)
+    w = window
+    cases = [(690, 690 - w + 1, True), (690, 690 - w, False), (690, 690, True), (690, 691, False), (690, 690 - min(w - 1, 18), True),
+             (690, 690 - min(w - 1, 19), True), (w + 39, 40, True), (w + 39, 39, False), (39, 0, w >= 40), (39, 39 - min(w - 1, 23), True),
+             (max(w - 1, 39), max(w - 1, 39) - (w - 1), True)]
+    for qp, kp, visible in cases:
+        rows = torch.zeros(n, H * D + 2 * D + H * D)
+        rows[:, H * D:H * D + D], rows[:, H * D + D:H * D + 2 * D] = key, val
+        rows[qp, D:2 * D] = 40.0 * key[kp]  # head 1 aims at position kp; head 0 asks nothing
+        rows = rows.to(dtype).to(F32)
+        hi = max(qp, kp) + 1
+        start = qp - 39 if prompt else qp
+        bias = torch.zeros(H * D + 2 * D)
+        got = run_attention(lib, dtype, mx, [rows], bias, [start], [hi], gated=False)[qp - start]
+        want = oracle_attention(mx, rows, bias, qp, hi, gated=False)[0]
+        assert torch.allclose(got, want, atol=1e-4 if dtype == F32 else 6e-2), (qp, kp)
+        target = O.unit_rms(val[kp], EPS)
+        if visible:
+            assert torch.allclose(got[D:], target, atol=2e-2 if dtype == F32 else 8e-2), (qp, kp)
+        else:
+            assert (got[D:] - target).norm() > 0.5 * target.norm(), (qp, kp)
+
+
+def test_attention_sink_of_score_zero_and_soft_cap_arithmetic(lib):
+    """one visible key: weight e^s / (1 + e^s) with s = cap * tanh(raw / cap) - slope * 0; two keys: the older one loses slope * 1"""
+    D = 16
+    mx = attn(1, 1, D, D, 0, cap=4.0, scale=0.5)["mixer"]
+    k0 = torch.nn.functional.normalize(torch.ones(D), dim=0)
+    rows = torch.zeros(2, D * 4)
+    rows[:, D:2 * D] = k0
+    rows[0, 2 * D:3 * D], rows[1, 2 * D:3 * D] = torch.arange(D) - 7.5, torch.ones(D)
+    rows[:, :D] = 12.0 * k0  # raw score 12 * 0.5 = 6 -> capped to 4 tanh(1.5)
+    got = run_attention(lib, F32, mx, [rows], torch.zeros(3 * D), [0], [2], gated=False)
+    s = 4.0 * math.tanh(1.5)
+    v0, v1 = O.unit_rms(rows[0, 2 * D:3 * D], EPS), O.unit_rms(rows[1, 2 * D:3 * D], EPS)
+    assert torch.allclose(got[0], math.exp(s) / (1 + math.exp(s)) * v0, atol=1e-5)
+    slope = 2.0 ** -8.0
+    e0, e1 = math.exp(s - slope), math.exp(s)
+    assert torch.allclose(got[1], (e0 * v0 + e1 * v1) / (1 + e0 + e1), atol=1e-5)
+
+
+def freq_table(rot):
+    i = torch.arange(rot["dims"] // 2, dtype=torch.float64)
+    return (rot["base"] ** (-2.0 * i / max(rot["dims"], 1))).to(F32).cuda()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_interleaved_rotation_of_a_slice_and_of_the_cached_key_part(lib, dtype):
+    P = Hold()
+    T, H, width, dims, keep, rank, ps = 6, 3, 10, 6, 7, 20, 4
+    rot = {"dims": dims, "base": 700.0}
+    g = torch.Generator().manual_seed(5)
+    pos = [0, 1, 5, 6, 7, 300]
+    x = torch.randn(T, H, keep + width, generator=g).to(dtype).to(F32)
+    f = freq_table(rot)
+    out = torch.zeros(T, H, rank + width, dtype=dtype, device="cuda")
+    f32 = int(dtype == F32)
+    assert lib.pk_rope_slice_ex(P(dev(x, dtype)), out.data_ptr(), P(i32(pos)), f.data_ptr(), 1.0, T, H, keep + width, keep, rank + width, rank, width, dims, 1,
+                                f32, None) == 0
+    torch.cuda.synchronize()
+    tol = 1e-5 if dtype == F32 else 2e-2
+    assert torch.allclose(out[..., rank:].float().cpu(), O.rotate_pairs(x[..., keep:], torch.tensor(pos), rot), atol=tol, rtol=tol)
+    # append: normed latent + rotated key part into scrambled pages
+    dkv = torch.randn(T, rank + width, generator=g).to(dtype).to(F32)
+    nw = (1 + 0.3 * torch.randn(rank, generator=g)).to(dtype).to(F32)
+    pages, off, n_pages = paged([301], ps)
+    stride = ps * (rank + width) + 8
+    cache = torch.zeros(n_pages, stride, dtype=dtype, device="cuda")
+    assert lib.pk_latent_kv_append_ex(P(dev(dkv, dtype)), P(dev(nw, dtype)), P(i32(pos)), P(i32([0] * T)), P(i32(off)), P(i32(pages)), cache.data_ptr(), stride,
+                                      ps, rank, width, dims, 1, f.data_ptr(), 1.0, EPS, T, f32, None) == 0
+    torch.cuda.synchronize()
+    c, kr = O.unit_rms(dkv[:, :rank], EPS) * nw, O.rotate_pairs(dkv[:, rank:], torch.tensor(pos), rot)
+    got = cache.float().cpu()
+    for t, p in enumerate(pos):
+        line = got[pages[p // ps], (p % ps) * (rank + width):(p % ps + 1) * (rank + width)]
+        assert torch.allclose(line[:rank], c[t], atol=tol, rtol=tol) and torch.allclose(line[rank:], kr[t], atol=tol, rtol=tol)
+
+
+def run_latent(lib, dtype, qa, c_all, kr_all, sink, pos, req, lens, scale, window, ps=16):
+    """qa [T, H, rank + rot] (queries folded onto the latent); request r's cache lines c_all[r] [len, rank], kr_all[r] [len, rot]"""
+    P = Hold()
+    T, H, Dq = qa.shape
+    rank = c_all[0].shape[1]
+    pages, off, n_pages = paged(lens, ps, shuffle_seed=5)
+    stride = ps * Dq + 16
+    cache = torch.zeros(n_pages, stride, dtype=dtype)
+    for r, n in enumerate(lens):
+        for p in range(n):
+            page, slot = pages[off[r] + p // ps], p % ps
+            cache[page, slot * Dq:slot * Dq + rank] = c_all[r][p].to(dtype)
+            cache[page, slot * Dq + rank:(slot + 1) * Dq] = kr_all[r][p].to(dtype)
+    out = torch.zeros(T, H, rank, dtype=dtype, device="cuda")
+    rc = lib.pk_latent_attention_ex(P(dev(qa, dtype)), P(cache.cuda()), P(dev(sink, dtype)) if sink is not None else None, P(i32(pos)), P(i32(req)), P(i32(off)),
+                                    P(i32(pages)), out.data_ptr(), stride, ps, T, H, rank, Dq - rank, scale, window, max(lens), int(dtype == F32), None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    return out.float().cpu()
+
+
+def dense_latent(qa, c, kr, pos, scale, window, sink=None):
+    """softmax over the visible cache lines of (qa . [c | kr]) * scale, values c (optionally exp(sink) in the denominator)"""
+    keys = torch.cat([c, kr], 1)
+    ok = O.visible(torch.tensor(pos), torch.arange(c.shape[0]), window)
+    out = []
+    for h in range(qa.shape[1]):
+        s = torch.where(ok, (qa[:, h] @ keys.T) * scale, torch.full((len(pos), c.shape[0]), -float("inf")))
+        if sink is not None:
+            s = torch.cat([s, sink[h].expand(len(pos), 1)], 1)
+        p = torch.softmax(s, -1)[:, :c.shape[0]]
+        out.append(p @ c)
+    return torch.stack(out, 1)
+
+
+# (heads, rank, rot): bf16 with rank % 64 == 0 and rot % 16 == 0 runs the tensor-core kernel, the others the generic one
+LATENT_SHAPES = [(3, 40, 12), (7, 64, 48), (16, 128, 0), (20, 128, 16), (5, 256, 64), (2, 48, 8)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("window", [0, 29, 64])
+@pytest.mark.parametrize("H,rank,rot_w", LATENT_SHAPES)
+def test_latent_attention_with_a_window_ragged_batch(lib, dtype, H, rank, rot_w, window):
+    """three requests in one launch: a 40-token portion that starts at position 90, one decoded token at position 199, and the first
+    5 tokens of a sequence; ordinary softmax (no sink)"""
+    scale = 0.17
+    g = torch.Generator().manual_seed(3)
+    lens = [130, 200, 5]
+    c = [torch.randn(n, rank, generator=g).to(dtype).to(F32) for n in lens]
+    kr = [torch.randn(n, rot_w, generator=g).to(dtype).to(F32) for n in lens]
+    pos = list(range(90, 130)) + [199] + list(range(5))
+    req = [0] * 40 + [1] + [2] * 5
+    qa = (torch.randn(46, H, rank + rot_w, generator=g) * (2.0 / math.sqrt(rank / 40))).to(dtype).to(F32)
+    got = run_latent(lib, dtype, qa, c, kr, None, pos, req, lens, scale, window)
+    want = torch.cat([dense_latent(qa[:40], c[0], kr[0], pos[:40], scale, window), dense_latent(qa[40:41], c[1], kr[1], pos[40:41], scale, window),
+                      dense_latent(qa[41:], c[2], kr[2], pos[41:], scale, window)])
+    tol = 2e-5 if dtype == F32 else 3e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("window", [0, 700, 100])
+def test_latent_attention_few_rows_long_contexts_split_over_keys(lib, window):
+    """decoded tokens of two requests with 3000 and 1500 cached positions (bf16, tensor-core kernel): the key axis -- the window's
+    part of it -- is split over CTAs and merged, with and without a sink"""
+    H, rank, rot_w = 16, 128, 32
+    g = torch.Generator().manual_seed(6)
+    lens = [3000, 1500]
+    c = [torch.randn(n, rank, generator=g).to(BF16).to(F32) for n in lens]
+    kr = [torch.randn(n, rot_w, generator=g).to(BF16).to(F32) for n in lens]
+    qa = 0.5 * torch.randn(2, H, rank + rot_w, generator=g)
+    far = 2999 - (window - 1 if window else 2982)
+    qa[0, 3, :rank] = 0.25 * c[0][far]   # head 3 of request 0 looks at the oldest visible position
+    qa[1, 5, :rank] = 0.25 * c[1][1499]  # head 5 of request 1 at its own position
+    qa = qa.to(BF16).to(F32)
+    for sink in (None, torch.zeros(H)):
+        got = run_latent(lib, BF16, qa, c, kr, sink, [2999, 1499], [0, 1], lens, 1.0, window)
+        want = torch.cat([dense_latent(qa[:1], c[0], kr[0], [2999], 1.0, window, sink), dense_latent(qa[1:], c[1], kr[1], [1499], 1.0, window, sink)])
+        assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
+        assert torch.allclose(got[0, 3], c[0][far], atol=5e-2) and torch.allclose(got[1, 5], c[1][1499], atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype,rank,rot_w", [(F32, 32, 8), (BF16, 32, 8), (BF16, 64, 16)])
+@pytest.mark.parametrize("prompt", [False, True])
+def test_latent_attention_single_keys_at_the_windows_edges(lib, dtype, rank, rot_w, prompt):
+    """One key carries the whole score: the output must be that key's latent -- the oldest key inside the window, both sides of page
+    borders, the query's own position, the first tokens.  The key just behind the window and the one after the query must not be seen."""
+    H, n = 2, 700
+    g = torch.Generator().manual_seed(4)
+    c = torch.nn.functional.normalize(torch.randn(n, rank, generator=g), dim=1).to(dtype).to(F32)
+    kr = (0.01 * torch.randn(n, rot_w, generator=g)).to(dtype).to(F32)
+    tol = 2e-3 if dtype == F32 else 4e-2
+    for window in (300, 48, 3):
+        w = window
+        cases = [(650, 650 - w + 1, True), (650, 650 - w, False), (650, 650, True), (650, 651, False), (650, 650 - min(w - 1, 10), True),
+                 (650, 650 - min(w - 1, 11), True), (w + 20, 21, True), (w + 20, 20, False), (2, 0, True), (0, 0, True)]
+        for qpos, target, seen in cases:
+            rows = 33 if prompt and qpos >= 32 else 1
+            qa = torch.zeros(rows, H, rank + rot_w)
+            qa[-1, :, :rank] = 60.0 * c[target]
+            pos = list(range(qpos - rows + 1, qpos + 1))
+            got = run_latent(lib, dtype, qa.to(dtype).to(F32), [c], [kr], None, pos, [0] * rows, [n], 1.0, window)[-1, 0]
+            if seen:
+                assert torch.allclose(got, c[target], atol=tol), (window, qpos, target)
+            else:
+                assert (got - c[target]).norm() > 0.5, (window, qpos, target)
+
+
+# ------------------------------------------------------------------ one mechanism per model
+MIXERS = {"attention": attn(3, 1, 16, 24, 21), "attention_wide": attn(2, 1, 160, 72, 50, cap=10.0), "attention_tile": attn(4, 2, 64, 64, 30),
+          "latent": latent(3, 16, 8, 24, 20, 21, rot_dims=6), "latent_tile": latent(4, 32, 16, 16, 64, 30), "latent_no_rotation": latent(2, 8, 0, 8, 24, 11)}
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(MIXERS))
+def test_one_mixer_alone(name, dtype):
+    """a one-layer model without feed-forward: the residual after the layer is x0 + m * norm(gated mixer(norm(x0)))"""
+    cfg = model_cfg([(MIXERS[name], 0)], vocab=64, width=48, groups=3)
+    w = make_weights(cfg, 11, 2.0)
+    toks = tokens_for(cfg, 75, 1)
+    m = build(cfg, w, dtype)
+    m.keep_trail(True)
+    rid = m.alloc_request()
+    m.step([(rid, toks)], [[len(toks) - 1]])
+    got = m.trail(len(toks))[0]
+    trail = []
+    oracle_logits(cfg, w, toks, trail)
+    x0 = O.group_norm(O.f32(w["embed"])[torch.tensor(toks)], O.f32(w["embed.norm"]), 3, 1e-5)
+    err = (got - trail[0]).abs().max() / (trail[0] - x0).abs().max()
+    assert err < (2e-5 if dtype == F32 else 4e-2)
+    m.close()
+
+
+# ------------------------------------------------------------------ the model through its own entry points
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_prompt_with_residual_after_every_layer(name, dtype):
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 21, sharp_for(name, dtype))
+    toks = tokens_for(cfg, 150, 2)
+    m = build(cfg, w, dtype)
+    m.keep_trail(True)
+    rid = m.alloc_request()
+    got = m.step([(rid, toks)], [list(range(len(toks)))])
+    trail = []
+    want = oracle_logits(cfg, w, toks, trail)
+    tr = m.trail(len(toks))
+    for i, x in enumerate(trail):
+        e = (tr[i] - x).abs().max() / x.abs().max()
+        assert e < (1e-4 if dtype == F32 else 0.2), (i, e)
+    assert close(got, want, dtype)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_prefill_against_token_by_token_decoding(name, dtype):
+    """the first tokens as one prompt, the rest one by one through the cache (every layer's window passes over decoded tokens);
+    then the same sequence decoded from its very first token"""
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 22, sharp_for(name, dtype))
+    toks = tokens_for(cfg, 130, 3)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    for first in (60, 1):
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:first])], [list(range(first))])]
+        for t in range(first, len(toks)):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert close(torch.cat(rows), want, dtype), first
+        m.drop_request(rid)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("sizes", [(2,), (3, 2, 16, 1, 37, 5), (64, 2, 2), (33, 1)])
+@pytest.mark.parametrize("name", ["general", "tiles"])
+def test_prompt_in_portions(name, dtype, sizes):
+    """portions cut anywhere (inside pages and windows), down to two tokens"""
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 23, SHARP[dtype])
+    toks = tokens_for(cfg, 140, 4)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    rows, at, k = [], 0, 0
+    while at < len(toks):
+        n = min(sizes[k % len(sizes)], len(toks) - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at, k = at + n, k + 1
+    assert close(torch.cat(rows), want, dtype)
+    m.close()
+
+
+def random_cfg(seed):
+    """layer order, every size and every constant drawn at random (seeded)"""
+    r = random.Random(seed)
+    width = r.choice([24, 36, 40, 64, 96, 120])
+    layers = []
+    for _ in range(r.randint(2, 6)):
+        heads = r.choice([1, 2, 3, 4, 6, 8])
+        window = r.choice([0, 1, 2, 7, 16, 31, 48, 64, 90, 200])
+        if r.random() < 0.55:
+            kv = r.choice([d for d in (1, 2, 3, 4, 6, 8) if heads % d == 0])
+            dim = r.choice([8, 12, 20, 32, 40, 64, 96, 128])
+            vdim = dim if r.random() < 0.6 else r.choice([8, 16, 28, 48])
+            l = attn(heads, kv, dim, vdim, window, cap=r.choice([0.0, 5.0, 20.0, 80.0]), scale=r.uniform(0.05, 0.4))
+        else:
+            rot_dim = r.choice([0, 4, 8, 16, 32])
+            l = latent(heads, r.choice([8, 12, 24, 32, 64]), rot_dim, r.choice([8, 20, 32, 64]), r.choice([16, 24, 40, 64, 128]), window,
+                       rot_dims=r.choice([0, rot_dim // 2 // 2 * 2, rot_dim]), base=r.choice([100.0, 10000.0, 1e6]), scale=r.uniform(0.05, 0.4))
+        layers.append((l, r.choice([0, 8, 20, 32, 44, 64])))
+    return model_cfg(layers, vocab=r.randint(40, 300), width=width, eps=r.choice([1e-5, 1e-6]), groups=r.choice([g for g in (1, 2, 3, 4, 6, 8, 12) if width % g == 0 and width // g >= 6]),
+                     mult=r.uniform(0.3, 1.5), logit=r.uniform(0.2, 2.0))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("seed", range(14))
+def test_configurations_drawn_at_random(seed, dtype):
+    """a prompt in portions of random sizes (some >= 32 tokens, so that the tensor-core kernels run where the sizes allow), then
+    decoded tokens, against the oracle over the whole sequence"""
+    cfg = random_cfg(100 + seed)
+    w = make_weights(cfg, 200 + seed, SHARP[dtype])
+    toks = tokens_for(cfg, 120, seed)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    r = random.Random(seed)
+    rows, at = [], 0
+    while at < len(toks):
+        n = 1 if at >= 100 else min(r.choice([1, 2, 5, 17, 33, 48]), 100 - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at += n
+    assert close(torch.cat(rows), want, dtype), cfg
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", ["general", "tiles"])
+def test_unequal_batches_reuse_pages_and_slots(name, dtype):
+    """Seven unequal requests through three request slots and a pool of 18 pages: portions of some beside single tokens of others in
+    every step; finished requests hand their pages and slot to the next one.  Every request must come out as when it runs alone."""
+    from pegainfer_b200.engine import Engine
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 24, SHARP[dtype])
+    lens = [70, 9, 40, 101, 1, 33, 64]
+    prompts = [tokens_for(cfg, n, 30 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, p) for p in prompts]
+    m = build(cfg, w, dtype, max_tokens=18 * 16, max_requests=3)
+    eng = Engine(m)
+    got = [[] for _ in prompts]
+    at = [0] * len(prompts)
+    waiting, live, step, seen_pages = list(range(len(prompts))), [], 0, set()
+    portion = [5, 1, 17, 2, 1, 40, 3]
+    pages_of = lambda i: (lens[i] + 15) // 16  # noqa: E731
+    while waiting or live:
+        while waiting and len(live) < 3 and sum(pages_of(i) for i in live) + pages_of(waiting[0]) <= 18:
+            live.append(waiting.pop(0))
+        entries = []
+        for i in live:
+            n = min(portion[(step + i) % len(portion)], lens[i] - at[i])
+            entries.append((f"q{i}", prompts[i][at[i]:at[i] + n], list(range(n))))
+        out = eng.step(entries, [])
+        r = 0
+        for (name_, t, _), i in zip(entries, list(live)):
+            got[i].append(out[r:r + len(t)])
+            r += len(t)
+            at[i] += len(t)
+            seen_pages.update(m.request_pages(eng.slots[name_]))
+            if at[i] == lens[i]:
+                eng.release(name_)
+                live.remove(i)
+        step += 1
+    assert sum((n + 15) // 16 for n in lens) > 18 >= len(seen_pages)  # pages were handed out again
+    for i in range(len(prompts)):
+        assert close(torch.cat(got[i]), want[i], dtype), i
+    m.close()
+
+
+def test_rejected_step_leaves_lengths_and_pages_untouched():
+    cfg = cfg_general()
+    w = make_weights(cfg, 25)
+    toks = tokens_for(cfg, 60, 5)
+    m = build(cfg, w, F32, max_tokens=64, max_requests=2)
+    a, b = m.alloc_request(), m.alloc_request()
+    m.step([(a, toks[:20])])
+    free = m.available_pages()
+    with pytest.raises(RuntimeError):
+        m.step([(a, toks[20:25]), (b, toks[:60])])  # b does not fit: nothing of the step may stay
+    assert m.seq_len(a) == 20 and m.seq_len(b) == 0 and m.available_pages() == free
+    got = m.step([(a, toks[20:40])], [list(range(20))])
+    assert close(got, oracle_logits(cfg, w, toks[:40])[20:], F32)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_long_decoding_and_captured_steps(dtype):
+    """a 300-token prompt and 260 decoded tokens (captured launch sequences from the second step of a kind on, across a graph bucket
+    border at 512; windows of 100 and 130 tokens leave the prompt behind while decoding) against the same steps run eagerly and
+    against the oracle"""
+    cfg = model_cfg([(attn(4, 2, 32, 32, 100), 32), (latent(2, 32, 16, 32, 64, 130), 0), (attn(2, 1, 24, 40, 0), 48)], vocab=96, width=64)
+    w = make_weights(cfg, 26, SHARP[dtype])
+    toks = tokens_for(cfg, 560, 6)
+    outs = []
+    for graph in (True, False):
+        m = build(cfg, w, dtype, max_tokens=1024)
+        m.use_graph(graph)
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:300])])]
+        for t in range(300, 560):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert (m.graph_count() > 0) == graph
+        outs.append(torch.cat(rows))
+        m.close()
+    assert torch.allclose(outs[0], outs[1], atol=1e-5 if dtype == F32 else 2e-2)
+    want = oracle_logits(cfg, w, toks)[299:]
+    assert close(outs[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_far_key_inside_a_long_window(dtype):
+    """a 900-token prompt under windows of 800 tokens, then 60 decoded tokens: sharpened queries make single far keys count"""
+    cfg = model_cfg([(attn(2, 1, 32, 32, 800, cap=25.0), 32), (latent(2, 16, 16, 32, 64, 800), 32)], vocab=120, width=48, groups=2)
+    w = make_weights(cfg, 31, 6.0 if dtype == F32 else 3.0)
+    toks = tokens_for(cfg, 960, 8)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype, max_tokens=1024)
+    rid = m.alloc_request()
+    rows = [m.step([(rid, toks[:900])], [list(range(700, 900))])]
+    for t in range(900, 960):
+        rows.append(m.step([(rid, [toks[t]])]))
+    assert close(torch.cat(rows), want[700:], dtype)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_batched_decode_steps_of_unequal_requests(dtype):
+    """three prompts of unequal length admitted in one step, then 40 steps that carry one token of each (replayed as a captured
+    launch sequence from the third step on); every request must come out as when it runs alone"""
+    cfg = cfg_general()
+    w = make_weights(cfg, 29, SHARP[dtype])
+    lens = [23, 61, 4]
+    seqs = [tokens_for(cfg, n + 40, 50 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, q) for q in seqs]
+    m = build(cfg, w, dtype)
+    rids = [m.alloc_request() for _ in lens]
+    got = [[] for _ in lens]
+    out = m.step([(r, q[:n]) for r, q, n in zip(rids, seqs, lens)])
+    for i in range(3):
+        got[i].append(out[i:i + 1])
+    for t in range(40):
+        out = m.step([(r, [q[n + t]]) for r, q, n in zip(rids, seqs, lens)])
+        for i in range(3):
+            got[i].append(out[i:i + 1])
+    assert m.graph_count() > 0
+    for i, n in enumerate(lens):
+        assert close(torch.cat(got[i]), want[i][n - 1:], dtype), i
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_greedy_generation_through_the_scheduler(dtype):
+    """the framework's own entry points: generate() of the model and the continuous-batching scheduler; teacher-forced check of
+    every generated token against the oracle's logits for the sequence the framework produced"""
+    from pegainfer_b200.engine import Engine
+    cfg = cfg_general()
+    w = make_weights(cfg, 27)
+    prompts = [tokens_for(cfg, n, 40 + n) for n in (5, 37, 1, 64, 18)]
+    m = build(cfg, w, dtype, max_tokens=512, max_requests=3)
+    outs = Engine(m).generate(prompts, 12, max_live=3, token_budget=48)
+    alone, _, _ = m.generate(prompts[1], 12)
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        lg = oracle_logits(cfg, w, p + o[:-1])[len(p) - 1:]
+        top2 = lg.topk(2, -1).values
+        gap_ok = (top2[:, 0] - top2[:, 1]) < (1e-3 if dtype == F32 else 0.15) * lg.std()
+        assert ((lg.argmax(-1) == torch.tensor(o)) | gap_ok).all()
+    if dtype == F32:
+        assert alone == outs[1]
+    m.close()
+
+
+def test_checkpoint_folder_through_the_registry_and_the_trace_tool(tmp_path):
+    """a checkpoint folder loaded by what its config.json says; the same folder replayed by bin/trace_run in a process of its own"""
+    import json
+    import os
+    import subprocess
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    from pegainfer_b200.registry import architecture_of, load_model
+    cfg = cfg_edges()
+    w = make_weights(cfg, 28)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    assert architecture_of(str(tmp_path)) == "Nagosun"
+    toks = tokens_for(cfg, 40, 7)
+    want = oracle_logits(cfg, w, toks)
+    m = load_model(str(tmp_path), "float32", max_tokens=256)
+    rid = m.alloc_request()
+    assert close(m.step([(rid, toks)], [list(range(40))]), want, F32)
+    m.close()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:25], "want": [3, 24]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[25:27], "want": []}, {"id": "b", "tokens": toks[:9], "want": [8]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[27:28], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    rows = {0: [3, 24], 1: [8], 2: [27]}
+    assert not (out / "3.f32").exists()
+    for s, idx in rows.items():
+        got = torch.from_numpy(np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(len(idx), -1).copy())
+        assert close(got, want[torch.tensor(idx)], F32), s
