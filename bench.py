@@ -791,6 +791,22 @@ def _risolorn_sizes():
     return {"w2048": ris(2048, 16, 4, 128, 1024, 64, 6, 8, 4, 1408, 32768), "w1024": ris(1024, 8, 2, 64, 1024, 16, 2, 4, 2, 768, 32768)}
 
 
+def _nagosun_sizes():
+    """Nagosun stacks of the same width, head count, head size, feed-forward width and vocabulary as the Qwen3 stacks of `_arch_sizes`
+    (its closest relative: grouped-query attention + dense SwiGLU), with one latent-attention layer shaped like the Vamadra stack's:
+    attention, attention, latent attention, attention; sliding windows of 1024 tokens."""
+    def nag(width, heads, kv, dim, ff, lat, vocab, window=1024):
+        att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+               "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "scale": dim ** -0.5, "softcap": 30.0}}
+        ldim, lrot, lv, rank = lat
+        la = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": heads, "dim": ldim, "rot_dim": lrot, "vdim": lv, "kv_rank": rank, "mask": {"size": window}, "scale": (ldim + lrot) ** -0.5,
+                        "rot": {"dims": lrot, "base": 10000.0}}}
+        return {"architecture": "Nagosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 8}, "residual_mult": 0.5, "logit_scale": 1.0,
+                "layers": [att, att, la, att]}
+    return {"w2048": nag(2048, 16, 8, 128, 6 * 1408 + 2816, (128, 64, 128, 512), 32768), "w1024": nag(1024, 8, 4, 128, 2 * 768 + 1536, (64, 32, 64, 256), 32768)}
+
+
 def _measure_layered(vm, prompts, ctx, med, synthetic_prompt):
     """prefill tok/s per prompt length and decode tok/s at batch 1 and 4 of a model on the layer-list host"""
     res = {}
@@ -818,8 +834,8 @@ def _measure_layered(vm, prompts, ctx, med, synthetic_prompt):
 
 
 def run_arch_compare(args):
-    """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  `--arch risolorn`:
-    the Risolorn path beside both.  Wall clock around each public-API call (token ids from the host in, logits / token back out,
+    """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  `--arch risolorn` /
+    `--arch nagosun`: that design's path beside both.  Wall clock around each public-API call (token ids from the host in, logits / token back out,
     stream synchronised), median of the repeats after warm-up; between repeats nothing else runs on the GPU.  One JSON line."""
     import torch
     from pegainfer_b200.model import ModelRuntimeConfig, Qwen3Model
@@ -852,6 +868,12 @@ def run_arch_compare(args):
             rm = RisolornModel(rcfg, ris_weights(rcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
             row["risolorn"] = _measure_layered(rm, prompts, ctx, med, synthetic_prompt)
             rm.close()
+        if args.arch == "nagosun":
+            from pegainfer_b200.nagosun import NagosunConfig, NagosunModel, iter_random_weights as nag_weights
+            ncfg = NagosunConfig.from_dict(_nagosun_sizes()[name])
+            nm = NagosunModel(ncfg, nag_weights(ncfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
+            row["nagosun"] = _measure_layered(nm, prompts, ctx, med, synthetic_prompt)
+            nm.close()
         vcfg = VamadraConfig.from_dict(vcfg_d)
         vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
         row["vamadra"] = _measure_layered(vm, prompts, ctx, med, synthetic_prompt)
@@ -898,7 +920,7 @@ def main():
     ap.add_argument("--weights", default="cpu", choices=["cpu", "cuda"],
                     help="cpu (default): the seed-0 CPU checkpoint the oracle fixtures were computed on; cuda: generated on "
                          "each GPU (fast; tuning sweeps only -- the parity key then reports a different checkpoint)")
-    ap.add_argument("--arch", default=None, choices=["vamadra", "risolorn"],
+    ap.add_argument("--arch", default=None, choices=["vamadra", "risolorn", "nagosun"],
                     help="instead of the headline workload: prefill / decode throughput of this design beside the closest existing ones at equal size")
     ap.add_argument("--arch-size", default=None, help="with --arch: comma-separated subset of the sizes (w2048,w1024)")
     args = ap.parse_args()

@@ -540,6 +540,7 @@ typedef struct pk_attn_extra {
   float slope_log2;  /* head h subtracts 2^(-slope_log2 (h + 1) / heads) * (p - j) from the (capped) score of key j */
   const void* gate;  /* element type, rows of stride gate_ld: out[t, h, d] *= logistic(gate[t * gate_ld + h * vdim + d]) */
   long gate_ld;
+  int max_kv_len;    /* longest context in the step (0 = unknown): lets a step of few rows split the key axis over CTAs */
 } pk_attn_extra;
 /* pk_gqa_attention with those options (extra == NULL: none).  A sink of score zero ("one added to the denominator") is a sink vector of zeros. */
 int pk_gqa_attention_ex(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,

@@ -79,6 +79,7 @@ struct AttnExtra {
   float softcap, slope_log2;
   const void* gate;
   long gate_ld;
+  int max_kv_len;
 };
 __device__ __forceinline__ int first_visible(int p, int chunk, int window) {
   int lo = chunk > 0 ? (p / chunk) * chunk : 0;
@@ -91,8 +92,14 @@ __device__ __forceinline__ float shape_score(float s, float softcap, float slope
   if (softcap > 0.f) s = softcap * tanhf(s / softcap);
   return s - slope * (float)distance;
 }
+// the same with tanh(z) = 1 - 2 / (e^(2z) + 1) on the fast exponential and division (absolute error of a few 1e-7: far below the
+// bf16 rounding of P in the tensor-core kernel, where every score of a tile pays for it)
+__device__ __forceinline__ float shape_score_fast(float s, float softcap, float inv_cap, float slope, int distance) {
+  if (softcap > 0.f) s = softcap * (1.f - __fdividef(2.f, __expf(2.f * s * inv_cap) + 1.f));
+  return s - slope * (float)distance;
+}
 
-constexpr int kGqaWarps = 4;
+constexpr int kGqaWarps = 8;
 constexpr int kGqaMaxPerLane = 8;  // features per lane: dim, vdim <= 256
 
 template <typename E>
@@ -118,24 +125,33 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  for (int j = lo + warp; j <= p; j += kGqaWarps) {
-    const E* kv = cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok;
-    const E* kr = kv + g * dim;
-    const E* vr = kv + G * dim + g * vdim;
-    float s = 0.f;
+  // two keys per trip (j and j + warps): their loads, dot products and exponentials overlap, which halves the dependent chain per key
+  for (int j = lo + warp; j <= p; j += 2 * kGqaWarps) {
+    const int j2 = j + kGqaWarps;
+    const bool two = j2 <= p;
+    const E* kv_a = cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok;
+    const E* kv_b = two ? cache + (size_t)pg[j2 / page_size] * page_stride + (size_t)(j2 % page_size) * tok : kv_a;
+    float ka[kGqaMaxPerLane], kb[kGqaMaxPerLane], va[kGqaMaxPerLane], vb[kGqaMaxPerLane];
 #pragma unroll
     for (int i = 0; i < kGqaMaxPerLane; ++i) {
       const int d = lane + 32 * i;
-      if (d < dim) s = fmaf(qr[i], to_f(kr[d]), s);
+      ka[i] = d < dim ? to_f(kv_a[g * dim + d]) : 0.f;
+      kb[i] = d < dim ? to_f(kv_b[g * dim + d]) : 0.f;
+      va[i] = d < vdim ? to_f(kv_a[G * dim + g * vdim + d]) : 0.f;
+      vb[i] = d < vdim ? to_f(kv_b[G * dim + g * vdim + d]) : 0.f;
     }
-    s = shape_score(warp_sum(s), x.softcap, slope, p - j);
-    const float mn = fmaxf(m, s), c = expf(m - mn), e = expf(s - mn);
-    l = l * c + e;
+    float sa = 0.f, sb = 0.f;
 #pragma unroll
     for (int i = 0; i < kGqaMaxPerLane; ++i) {
-      const int d = lane + 32 * i;
-      if (d < vdim) acc[i] = acc[i] * c + e * to_f(vr[d]);
+      sa = fmaf(qr[i], ka[i], sa);
+      sb = fmaf(qr[i], kb[i], sb);
     }
+    sa = shape_score(warp_sum(sa), x.softcap, slope, p - j);
+    sb = two ? shape_score(warp_sum(sb), x.softcap, slope, p - j2) : -INFINITY;
+    const float mn = fmaxf(m, fmaxf(sa, sb)), c = expf(m - mn), ea = expf(sa - mn), eb = two ? expf(sb - mn) : 0.f;
+    l = l * c + (ea + eb);
+#pragma unroll
+    for (int i = 0; i < kGqaMaxPerLane; ++i) acc[i] = acc[i] * c + (ea * va[i] + eb * vb[i]);
     m = mn;
   }
   if (lane == 0) {
@@ -180,8 +196,9 @@ template <int DQ, int DV>
 __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const bf16* __restrict__ sink,
                                                                const int* __restrict__ pos, const int* __restrict__ req,
                                                                const int* __restrict__ page_off, const int* __restrict__ pages,
-                                                               bf16* __restrict__ out, long page_stride, int page_size, int T, int H, int G,
-                                                               float scale, int chunk, AttnExtra x) {
+                                                               bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                                                               long page_stride, int page_size, int T, int H, int G, float scale, int chunk,
+                                                               AttnExtra x) {
   constexpr int LDK = DQ + 8, LDV = DV + 8;
   extern __shared__ __align__(16) unsigned char am_smem[];  // two stages of [keys][LDK] K and [keys][LDV] V
   bf16* const Ks0 = reinterpret_cast<bf16*>(am_smem);
@@ -202,7 +219,8 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
   const int ra = warp * 16 + gq, rb = ra + 8;
   const int req_a = s_req[ra], req_b = s_req[rb], pos_a = s_pos[ra], pos_b = s_pos[rb];
   const int lo_a = pos_a >= 0 ? first_visible(pos_a, chunk, x.window) : 0, lo_b = pos_b >= 0 ? first_visible(pos_b, chunk, x.window) : 0;
-  const float slope = head_slope(x.slope_log2, h, H);
+  const float slope = head_slope(x.slope_log2, h, H), inv_cap = x.softcap > 0.f ? 1.f / x.softcap : 0.f;
+  const int split = blockIdx.z, nsplit = gridDim.z;  // few rows: every request's 64-key blocks are dealt out to gridDim.z CTAs
   // Q fragments (A operand, row-major 16 x DQ)
   uint32_t qa[DQ / 16][4];
 #pragma unroll
@@ -243,14 +261,16 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
       }
       cp_async_commit();
     };
-    const int k_first = k_lo - (k_lo % kAmKeys);
+    const int k_start = k_lo - (k_lo % kAmKeys);
+    const int n_blocks = (p_max - k_start) / kAmKeys + 1, per_split = (n_blocks + nsplit - 1) / nsplit;
+    const int k_first = k_start + split * per_split * kAmKeys, k_last = min(p_max, k_first + per_split * kAmKeys - 1);
     __syncthreads();  // the previous request's readers are done with both stages
-    load(k_first, 0);
-    for (int k0 = k_first, it = 0; k0 <= p_max; k0 += kAmKeys, ++it) {
+    if (k_first <= k_last) load(k_first, 0);
+    for (int k0 = k_first, it = 0; k0 <= k_last; k0 += kAmKeys, ++it) {
       const int buf = it & 1;
       cp_async_wait_all();
       __syncthreads();  // this block has landed, and nobody reads the other stage any more
-      if (k0 + kAmKeys <= p_max) load(k0 + kAmKeys, buf ^ 1);  // overlaps the products below
+      if (k0 + kAmKeys <= k_last) load(k0 + kAmKeys, buf ^ 1);  // overlaps the products below
       const bf16* Ks = Ks0 + buf * kAmKeys * LDK;
       const bf16* Vs = Vs0 + buf * kAmKeys * LDV;
       const bool on_a = req_a == rq, on_b = req_b == rq;
@@ -274,7 +294,7 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
           const int j = k0 + ni * 8 + 2 * tq + (e & 1);
           const bool top = e < 2;
           const bool ok = top ? (on_a && j <= pos_a && j >= lo_a) : (on_b && j <= pos_b && j >= lo_b);
-          const float v = ok ? shape_score(s[ni][e] * scale, x.softcap, slope, (top ? pos_a : pos_b) - j) : -INFINITY;
+          const float v = ok ? shape_score_fast(s[ni][e] * scale, x.softcap, inv_cap, slope, (top ? pos_a : pos_b) - j) : -INFINITY;
           s[ni][e] = v;
           if (top) mx_a = fmaxf(mx_a, v);
           else mx_b = fmaxf(mx_b, v);
@@ -325,6 +345,18 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
     }
     r_first = r_last + 1;
   }
+  if (nsplit > 1) {  // partial state (running maximum, sum, unnormalised output) of this split; gqa_attention_merge_kernel finishes the rows
+    const size_t sa = ((size_t)(h * nsplit + split) * T + (t0 + ra)), sb = ((size_t)(h * nsplit + split) * T + (t0 + rb));
+    if (req_a >= 0 && tq == 0) part_ml[sa * 2] = m_a, part_ml[sa * 2 + 1] = l_a;
+    if (req_b >= 0 && tq == 0) part_ml[sb * 2] = m_b, part_ml[sb * 2 + 1] = l_b;
+#pragma unroll
+    for (int ni = 0; ni < DV / 8; ++ni) {
+      const int c = ni * 8 + 2 * tq;
+      if (req_a >= 0) *reinterpret_cast<float2*>(part_o + sa * DV + c) = make_float2(oa[ni][0], oa[ni][1]);
+      if (req_b >= 0) *reinterpret_cast<float2*>(part_o + sb * DV + c) = make_float2(oa[ni][2], oa[ni][3]);
+    }
+    return;
+  }
   const float sk = sink ? bf2f(sink[h]) : -INFINITY;
   const float mt_a = fmaxf(m_a, sk), mt_b = fmaxf(m_b, sk);
   const float f_a = m_a == -INFINITY ? 0.f : expf(m_a - mt_a), f_b = m_b == -INFINITY ? 0.f : expf(m_b - mt_b);
@@ -345,6 +377,38 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
   }
 }
 
+// one CTA per (row, head): combine the splits' (m, l, O), join the sink, apply the output gate
+__global__ void gqa_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const bf16* __restrict__ sink,
+                                           bf16* __restrict__ out, int nsplit, int T, int H, int vdim, AttnExtra x) {
+  __shared__ float wgt[64];  // per split: exp(m_s - M) / denominator
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, h = blockIdx.y;
+  if (threadIdx.x < 32) {
+    const float sk = sink ? bf2f(sink[h]) : -INFINITY;
+    float m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int sp = threadIdx.x + 32 * i;
+      const size_t slot = (size_t)(h * nsplit + sp) * T + t;
+      m[i] = sp < nsplit ? part_ml[slot * 2] : -INFINITY;
+      l[i] = sp < nsplit ? part_ml[slot * 2 + 1] : 0.f;
+    }
+    const float M = fmaxf(warp_max(fmaxf(m[0], m[1])), sk);  // finite: a query always sees its own position
+    const float e0 = m[0] == -INFINITY ? 0.f : expf(m[0] - M), e1 = m[1] == -INFINITY ? 0.f : expf(m[1] - M);
+    const float inv = 1.f / (warp_sum(l[0] * e0 + l[1] * e1) + (sink ? expf(sk - M) : 0.f));
+    wgt[threadIdx.x] = e0 * inv;
+    wgt[threadIdx.x + 32] = e1 * inv;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float o = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) o = fmaf(part_o[((size_t)(h * nsplit + sp) * T + t) * vdim + d], wgt[sp], o);
+    if (x.gate) o *= 1.f / (1.f + expf(-bf2f(static_cast<const bf16*>(x.gate)[(size_t)t * x.gate_ld + h * vdim + d])));
+    out[((size_t)t * H + h) * vdim + d] = f2bf(o);
+  }
+}
+
 template <int DQ, int DV>
 static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off, const int* pages,
                            bf16* out, long page_stride, int page_size, int T, int H, int G, float scale, int chunk, AttnExtra x, cudaStream_t st) {
@@ -354,8 +418,25 @@ static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, c
     cudaFuncSetAttribute(gqa_attention_mma_kernel<DQ, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
-  launch(gqa_attention_mma_kernel<DQ, DV>, dim3((T + kAmRows - 1) / kAmRows, H), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out,
+  // Few rows (decode steps): the key axis is dealt out to several CTAs per (tile, head) so that the step fills the GPU.  The span a
+  // row can see is bounded by the window / chunk, else by the longest context of the step (when the caller knows it).
+  const int tiles = (T + kAmRows - 1) / kAmRows;
+  int span = x.max_kv_len;
+  if (x.window > 0) span = span > 0 ? min(span, x.window + T) : x.window + T;
+  if (chunk > 0) span = span > 0 ? min(span, chunk) : chunk;
+  int splits = 1;
+  ThreadState& ts = tls();
+  if (T < kAmRows && span > 2 * kAmKeys && ts.scratch) {
+    const int blocks = (span + kAmKeys - 1) / kAmKeys + 1;
+    splits = min(min(blocks, (2 * sm_count() + tiles * H - 1) / (tiles * H)), 64);
+    while (splits > 1 && (size_t)H * splits * T * (DV + 2) * sizeof(float) > ts.scratch_bytes) --splits;
+  }
+  float* po = static_cast<float*>(ts.scratch);
+  float* pml = po ? po + (size_t)H * splits * T * DV : nullptr;
+  launch(gqa_attention_mma_kernel<DQ, DV>, dim3(tiles, H, splits), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out, po, pml,
          page_stride, page_size, T, H, G, scale, chunk, x);
+  if (splits > 1)
+    launch(gqa_attention_merge_kernel, dim3(T, H), dim3(DV >= 128 ? 128 : 64), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, T, H, DV, x);
 }
 
 }  // namespace pk
@@ -401,15 +482,16 @@ extern "C" int pk_gqa_attention_ex(const void* q, const void* cache, const void*
   if (!q || !cache || !positions || !req || !page_off || !pages || !out || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       dim <= 0 || vdim <= 0 || chunk < 0 || page_size <= 0)
     return -1;
-  AttnExtra x{0, 0.f, 0.f, nullptr, 0};
+  AttnExtra x{0, 0.f, 0.f, nullptr, 0, 0};
   if (extra) {
-    if (extra->window < 0 || extra->softcap < 0.f || extra->slope_log2 < 0.f) return -1;
-    x = AttnExtra{extra->window, extra->softcap, extra->slope_log2, extra->gate, extra->gate_ld};
+    if (extra->window < 0 || extra->softcap < 0.f || extra->slope_log2 < 0.f || extra->max_kv_len < 0) return -1;
+    x = AttnExtra{extra->window, extra->softcap, extra->slope_log2, extra->gate, extra->gate_ld, extra->max_kv_len};
   }
   if (dim > 32 * kGqaMaxPerLane || vdim > 32 * kGqaMaxPerLane) return -2;
   const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                        page_stride % 8 == 0;
-  if (!f32 && tokens >= 32 && aligned && dim == vdim && (dim == 64 || dim == 128 || dim == 32 || dim == 96) && (dim * kv_heads) % 8 == 0) {
+  // bf16 prompt portions always; single decoded tokens too when the caller asked through the _ex entry (the key axis is then split)
+  if (!f32 && (tokens >= 32 || extra) && aligned && dim == vdim && (dim == 64 || dim == 128 || dim == 32 || dim == 96) && (dim * kv_heads) % 8 == 0) {
 #define PK_GQA_MMA(D) \
   launch_gqa_mma<D, D>((const bf16*)q, (const bf16*)cache, (const bf16*)sink, positions, req, page_off, pages, (bf16*)out, page_stride, page_size, tokens, heads, kv_heads, scale, chunk, x, st)
     if (dim == 32) PK_GQA_MMA(32);

@@ -908,6 +908,7 @@ bool Model::run_sandwich_layer(int li, int T, int max_kv, const int* M, int n) {
     ex.slope_log2 = a.slope_log2;
     ex.gate = ng ? (const char*)big.ptr + (size_t)(nq + nk + nv) * es : nullptr;
     ex.gate_ld = nbig;
+    ex.max_kv_len = max_kv;
     if (!rc(k.pk_gqa_attention_ex(q.ptr, pool_base, sink, d_pos, d_req, d_poff, d_pages, ao.ptr, page_stride, c.page_size, T, H, G, a.dim, a.vdim, a.scale,
                                   a.chunk, &ex, f32, st),
             "attention"))

@@ -362,8 +362,14 @@ __global__ void gnorm_rows_kernel(const float* __restrict__ x, const int* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)blockIdx.x * width + i] = from_f<E>(row[i] * inv_s[i / gsz] * to_f(w[i]));
 }
 
-constexpr int kGnormThreads = 256;
-static inline size_t gnorm_smem(int width, int groups) { return (size_t)(width + groups + std::max(groups, kGnormThreads / 32)) * sizeof(float); }
+// threads per row: about two entries per thread for a few rows (every dependent round of loads costs a memory latency, and a step of
+// one token is nothing but such rounds), 256 for many rows
+static inline int gnorm_threads(int width, int tokens) {
+  if (tokens > 64) return 256;
+  const int t = (width / 2 + 31) / 32 * 32;
+  return t < 128 ? 128 : t > 1024 ? 1024 : t;
+}
+static inline size_t gnorm_smem(int width, int groups) { return (size_t)(width + groups + std::max(groups, 32)) * sizeof(float); }
 template <typename K>
 static bool gnorm_fits(K kernel, size_t smem) {  // rows above 48 KB of shared memory need the opt-in limit (set once per kernel)
   if (smem <= 48 * 1024) return true;
@@ -507,9 +513,9 @@ extern "C" int pk_res32_embed_gnorm(const void* embed, const int* token_ids, con
   const size_t sm = gnorm_smem(width, groups);
   if (!(f32 ? gnorm_fits(embed_gnorm_kernel<float>, sm) : gnorm_fits(embed_gnorm_kernel<bf16>, sm))) return -2;
   PK_BY_TYPE(f32,
-             launch(embed_gnorm_kernel<float>, dim3(tokens), dim3(kGnormThreads), sm, st, true, (const float*)embed, token_ids, (const float*)w_embed, x,
+             launch(embed_gnorm_kernel<float>, dim3(tokens), dim3(gnorm_threads(width, tokens)), sm, st, true, (const float*)embed, token_ids, (const float*)w_embed, x,
                     (const float*)w_next, (float*)h, width, groups, eps),
-             launch(embed_gnorm_kernel<bf16>, dim3(tokens), dim3(kGnormThreads), sm, st, true, (const bf16*)embed, token_ids, (const bf16*)w_embed, x,
+             launch(embed_gnorm_kernel<bf16>, dim3(tokens), dim3(gnorm_threads(width, tokens)), sm, st, true, (const bf16*)embed, token_ids, (const bf16*)w_embed, x,
                     (const bf16*)w_next, (bf16*)h, width, groups, eps));
   return (int)cudaGetLastError();
 }
@@ -519,7 +525,7 @@ extern "C" int pk_res32_gated_gnorm_add(const void* y, int y_is_f32, const void*
                                         int tokens, int f32, pk_stream st) {
   if (!y || !w_post || !x || (w_next && !h) || width <= 0 || groups <= 0 || width % groups || tokens <= 0) return -1;
   const size_t sm = gnorm_smem(width, groups);
-  const dim3 g(tokens), b(kGnormThreads);
+  const dim3 g(tokens), b(gnorm_threads(width, tokens));
   if (f32) {
     if (!gnorm_fits(gated_gnorm_add_kernel<float, float>, sm)) return -2;
     launch(gated_gnorm_add_kernel<float, float>, g, b, sm, st, true, (const float*)y, (const float*)bias, (const float*)gate, gate_ld,
@@ -541,7 +547,7 @@ extern "C" int pk_res32_gnorm_rows(const float* x, const int* rows, const void* 
   if (!x || !w || !out || width <= 0 || groups <= 0 || width % groups || n_rows <= 0) return -1;
   const size_t sm = gnorm_smem(width, groups);
   if (!(f32 ? gnorm_fits(gnorm_rows_kernel<float>, sm) : gnorm_fits(gnorm_rows_kernel<bf16>, sm))) return -2;
-  PK_BY_TYPE(f32, launch(gnorm_rows_kernel<float>, dim3(n_rows), dim3(kGnormThreads), sm, st, true, x, rows, (const float*)w, (float*)out, width, groups, eps),
-             launch(gnorm_rows_kernel<bf16>, dim3(n_rows), dim3(kGnormThreads), sm, st, true, x, rows, (const bf16*)w, (bf16*)out, width, groups, eps));
+  PK_BY_TYPE(f32, launch(gnorm_rows_kernel<float>, dim3(n_rows), dim3(gnorm_threads(width, n_rows)), sm, st, true, x, rows, (const float*)w, (float*)out, width, groups, eps),
+             launch(gnorm_rows_kernel<bf16>, dim3(n_rows), dim3(gnorm_threads(width, n_rows)), sm, st, true, x, rows, (const bf16*)w, (bf16*)out, width, groups, eps));
   return (int)cudaGetLastError();
 }

@@ -113,7 +113,7 @@ i64l = C.c_long
 
 class AttnExtra(C.Structure):
     """pk_attn_extra: options of pk_gqa_attention_ex (a zero / NULL field switches its option off)."""
-    _fields_ = [("window", i32), ("softcap", f32), ("slope_log2", f32), ("gate", vp), ("gate_ld", i64l)]
+    _fields_ = [("window", i32), ("softcap", f32), ("slope_log2", f32), ("gate", vp), ("gate_ld", i64l), ("max_kv_len", i32)]
 
 
 RES32_SIGNATURES = {

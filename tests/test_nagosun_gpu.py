@@ -240,7 +240,7 @@ def paged(req_lens, page_size, shuffle_seed=0):
 EPS = 1e-5
 
 
-def run_attention(lib, dtype, mx, rows, bias, starts, lens, ps=16, gated=True):
+def run_attention(lib, dtype, mx, rows, bias, starts, lens, ps=16, gated=True, max_kv=0):
     """Bias + value norm + cache append + attention for a step whose request r brings positions starts[r] .. lens[r] - 1 (earlier
     positions were appended by a first call from rows of the same tensor).  rows: per request [len, nq + nk + nv + ng], the
     stacked projection outputs with the output gate's pre-activations last.  Returns [T, H * vdim]."""
@@ -267,7 +267,7 @@ def run_attention(lib, dtype, mx, rows, bias, starts, lens, ps=16, gated=True):
         assert lib.pk_gqa_rope_append_ex(xd.data_ptr(), ld, P(dev(bias, dtype)), *a, qo.data_ptr(), cache.data_ptr(), stride, ps, H, G, D, Dv, 0, 1, None, 1.0,
                                          EPS, T, f32, None) == 0
         ex = AttnExtra(window=int((mx.get("mask") or {}).get("size", 0)), softcap=float(mx.get("softcap") or 0.0), slope_log2=O.SLOPE_LOG2,
-                       gate=xd.data_ptr() + n_qkv * xd.element_size() if gated else None, gate_ld=ld)
+                       gate=xd.data_ptr() + n_qkv * xd.element_size() if gated else None, gate_ld=ld, max_kv_len=max_kv)
         assert lib.pk_gqa_attention_ex(qo.data_ptr(), cache.data_ptr(), zero_sink.data_ptr(), *a, out.data_ptr(), stride, ps, T, H, G, D, Dv,
                                        float(mx["scale"]), 0, C.byref(ex), f32, None) == 0
         torch.cuda.synchronize()
@@ -308,6 +308,26 @@ def test_attention_ragged_batch(lib, dtype, H, G, D, Dv, window, cap):
     bias = (0.3 * torch.randn(H * D + G * D + G * Dv, generator=g)).to(dtype).to(F32)
     got = run_attention(lib, dtype, mx, rows, bias, starts, lens)
     want = torch.cat([oracle_attention(mx, rows[r], bias, starts[r], lens[r]) for r in range(3)])
+    tol = 3e-5 if dtype == F32 else 4e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,D,window,known", [(4, 2, 128, 0, True), (4, 2, 128, 0, False), (6, 3, 64, 700, False), (2, 2, 96, 333, True), (3, 1, 40, 0, True)])
+def test_attention_decoded_tokens_of_long_contexts(lib, dtype, H, G, D, window, known):
+    """one decoded token of each of three requests with 1500, 130 and 2 cached positions in one launch (bf16 head sizes of the
+    tensor-core kernel: the key axis is dealt out to several CTAs and merged; without a window only when the caller names the
+    longest context)"""
+    mx = attn(H, G, D, D, window, cap=20.0)["mixer"]
+    g = torch.Generator().manual_seed(9)
+    lens = [1500, 130, 2]
+    n_all = H * D + 2 * G * D + H * D
+    rows = [torch.randn(n, n_all, generator=g).to(dtype).to(F32) for n in lens]
+    for x in rows:
+        x[:, :H * D] *= 2.0
+    bias = (0.3 * torch.randn(H * D + 2 * G * D, generator=g)).to(dtype).to(F32)
+    got = run_attention(lib, dtype, mx, rows, bias, [n - 1 for n in lens], lens, max_kv=1500 if known else 0)
+    want = torch.cat([oracle_attention(mx, rows[r], bias, lens[r] - 1, lens[r]) for r in range(3)])
     tol = 3e-5 if dtype == F32 else 4e-2
     assert torch.allclose(got, want, atol=tol, rtol=tol)
 
