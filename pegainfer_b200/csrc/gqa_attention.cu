@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
   bf16* const Ks0 = reinterpret_cast<bf16*>(am_smem);
   bf16* const Vs0 = Ks0 + 2 * kAmKeys * LDK;
   __shared__ int s_req[kAmRows], s_pos[kAmRows];
+  __shared__ long long s_slot[2][kAmKeys];  // per stage: element offset of every key row's cache slot (-1: not to be read)
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t0 = blockIdx.x * kAmRows, h = blockIdx.y, g = h / (H / G);
@@ -248,15 +249,23 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
     auto load = [&](int k0, int buf) {
       bf16* Kd = Ks0 + buf * kAmKeys * LDK;
       bf16* Vd = Vs0 + buf * kAmKeys * LDV;
+      if (tid < kAmKeys) {  // one page-table read per key row, not one per 16-byte piece
+        const int j = k0 + tid;
+        s_slot[buf][tid] = (j <= p_max && j >= k_lo) ? (long long)pg[j / page_size] * page_stride + (long long)(j % page_size) * tok : -1;
+      }
+      __syncthreads();
+#pragma unroll 4
       for (int c = tid; c < kAmKeys * (DQ / 8); c += 128) {
-        const int r = c / (DQ / 8), cc = (c % (DQ / 8)) * 8, j = k0 + r;
-        if (j <= p_max && j >= k_lo) cp_async16(&Kd[r * LDK + cc], cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + g * DQ + cc);
+        const int r = c / (DQ / 8), cc = (c % (DQ / 8)) * 8;
+        const long long at = s_slot[buf][r];
+        if (at >= 0) cp_async16(&Kd[r * LDK + cc], cache + at + g * DQ + cc);
         else *reinterpret_cast<uint4*>(&Kd[r * LDK + cc]) = make_uint4(0, 0, 0, 0);
       }
+#pragma unroll 4
       for (int c = tid; c < kAmKeys * (DV / 8); c += 128) {
-        const int r = c / (DV / 8), cc = (c % (DV / 8)) * 8, j = k0 + r;
-        if (j <= p_max && j >= k_lo)
-          cp_async16(&Vd[r * LDV + cc], cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + G * DQ + g * DV + cc);
+        const int r = c / (DV / 8), cc = (c % (DV / 8)) * 8;
+        const long long at = s_slot[buf][r];
+        if (at >= 0) cp_async16(&Vd[r * LDV + cc], cache + at + G * DQ + g * DV + cc);
         else *reinterpret_cast<uint4*>(&Vd[r * LDV + cc]) = make_uint4(0, 0, 0, 0);
       }
       cp_async_commit();
@@ -402,8 +411,17 @@ __global__ void gqa_attention_merge_kernel(const float* __restrict__ part_o, con
   }
   __syncthreads();
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
-    float o = 0.f;
-    for (int sp = 0; sp < nsplit; ++sp) o = fmaf(part_o[((size_t)(h * nsplit + sp) * T + t) * vdim + d], wgt[sp], o);
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    int sp = 0;
+    for (; sp + 4 <= nsplit; sp += 4) {  // the splits' loads are independent: four in flight
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = part_o[((size_t)(h * nsplit + sp + u) * T + t) * vdim + d];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) a4[u] = fmaf(v[u], wgt[sp + u], a4[u]);
+    }
+    for (; sp < nsplit; ++sp) a4[0] = fmaf(part_o[((size_t)(h * nsplit + sp) * T + t) * vdim + d], wgt[sp], a4[0]);
+    float o = (a4[0] + a4[1]) + (a4[2] + a4[3]);
     if (x.gate) o *= 1.f / (1.f + expf(-bf2f(static_cast<const bf16*>(x.gate)[(size_t)t * x.gate_ld + h * vdim + d])));
     out[((size_t)t * H + h) * vdim + d] = f2bf(o);
   }
