@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
 constexpr int kAmRows = 64, kAmKeys = 64;
 
 template <int DQ, int DV>
-__global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const bf16* __restrict__ sink,
+__global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const bf16* __restrict__ sink,
                                                                const int* __restrict__ pos, const int* __restrict__ req,
                                                                const int* __restrict__ page_off, const int* __restrict__ pages,
                                                                bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -207,7 +207,9 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
   __shared__ long long s_slot[2][kAmKeys];  // per stage: element offset of every key row's cache slot (-1: not to be read)
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
-  const int t0 = blockIdx.x * kAmRows, h = blockIdx.y, g = h / (H / G);
+  // grid (head, tile, split): the heads of a tile start together (a group's heads read the same keys), and the tiles run from the
+  // end of the step backwards, so that the CTAs that start last are the ones with the fewest visible keys
+  const int t0 = (gridDim.y - 1 - blockIdx.y) * kAmRows, h = blockIdx.x, g = h / (H / G);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
   if (tid < kAmRows) {
     const int t = t0 + tid;
@@ -451,7 +453,7 @@ static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, c
   }
   float* po = static_cast<float*>(ts.scratch);
   float* pml = po ? po + (size_t)H * splits * T * DV : nullptr;
-  launch(gqa_attention_mma_kernel<DQ, DV>, dim3(tiles, H, splits), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out, po, pml,
+  launch(gqa_attention_mma_kernel<DQ, DV>, dim3(H, tiles, splits), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out, po, pml,
          page_stride, page_size, T, H, G, scale, chunk, x);
   if (splits > 1)
     launch(gqa_attention_merge_kernel, dim3(T, H), dim3(DV >= 128 ? 128 : 64), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, T, H, DV, x);
