@@ -83,8 +83,8 @@ struct Lib {
   // every design / only the sequential latent-attention block form / only the parallel block form
 #define PV_COMMON(X)                                                                                                                       \
   X(cuda_set_device) X(cublas_init) X(cublas_destroy) X(gemm_cuda) X(flashinfer_top1_cuda) X(pk_b200_set_pdl) X(pk_b200_launch_count)      \
-  X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_proj_rows_f32out) \
-  X(pk_scale_to_f32) X(pk_moe_up_act) X(pk_moe_grouped_act) X(pk_top1_rows_f32)
+  X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_proj_rows_f32out) X(pk_scale_to_f32) X(pk_top1_rows_f32)
+#define PV_MOE(X) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_moe_up_act) X(pk_moe_grouped_act)
 #define PV_BLOCK0(X)                                                                                                                        \
   X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_act) X(pk_rope_slice) X(pk_latent_kv_append)             \
   X(pk_latent_attention) X(pk_router_grouped_topk) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
@@ -95,7 +95,7 @@ struct Lib {
   X(pk_res32_embed_gnorm) X(pk_res32_gated_gnorm_add) X(pk_res32_gnorm_rows) X(pk_gqa_rope_append_ex) X(pk_gqa_attention_ex) X(pk_rope_slice_ex)   \
   X(pk_latent_kv_append_ex) X(pk_latent_attention_ex) X(pk_act) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu) X(pk_b200_gemm_segments)
 #define PV_FN(name) decltype(&::name) name = nullptr;
-  PV_COMMON(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN)
+  PV_COMMON(PV_FN) PV_MOE(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN)
   // block 2 shares pk_act / pk_b200_gemv_fused / pk_b200_gemm_swiglu with block 0
   decltype(&::pk_res32_embed_gnorm) pk_res32_embed_gnorm = nullptr;
   decltype(&::pk_res32_gated_gnorm_add) pk_res32_gated_gnorm_add = nullptr;
@@ -117,10 +117,10 @@ struct Lib {
   if (!name) missing += std::string(" ") + #name;
     PV_COMMON(PV_REQ)
     if (block_kind == 0) {
-      PV_BLOCK0(PV_REQ)
+      PV_MOE(PV_REQ) PV_BLOCK0(PV_REQ)
     } else if (block_kind == 1) {
-      PV_BLOCK1(PV_REQ)
-    } else {
+      PV_MOE(PV_REQ) PV_BLOCK1(PV_REQ)
+    } else {  // the sandwich block form has no mixture of experts
       PV_BLOCK2(PV_REQ)
     }
 #undef PV_REQ
