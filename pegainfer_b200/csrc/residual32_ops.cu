@@ -307,6 +307,13 @@ __device__ __forceinline__ void st8(float* p, const float* v) {
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// logistic gate of a sublayer's result: exact in the all-fp32 build, on the fast exponential / division when activations are bf16
+template <typename E>
+__device__ __forceinline__ float gate_logistic(float z) {
+  if constexpr (sizeof(E) == 2) return __fdividef(1.f, 1.f + __expf(-z));
+  else return 1.f / (1.f + expf(-z));
+}
+
 // x[t] = gnorm(embed[ids[t]], w_embed);  h[t] = gnorm(x[t], w_next) in the element type (w_next may be null)
 template <typename E>
 __global__ void embed_gnorm_kernel(const E* __restrict__ embed, const int* __restrict__ tok, const E* __restrict__ w_embed, float* __restrict__ x,
@@ -362,7 +369,7 @@ __global__ void gated_gnorm_add_kernel(const Y* __restrict__ y, const E* __restr
           for (int u = 0; u < 8; ++u) z[u] += b[u];
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] *= 1.f / (1.f + expf(-z[u]));
+        for (int u = 0; u < 8; ++u) v[u] *= gate_logistic<E>(z[u]);
       }
       st8(row + i, v);
     }
@@ -372,8 +379,9 @@ __global__ void gated_gnorm_add_kernel(const Y* __restrict__ y, const E* __restr
       ld8(x + (size_t)t * width + i, xv);
       ld8(w_post + i, w);
       ld8(row + i, r);
+      const float inv = inv_s[i / gsz];  // the eight entries lie in one group (gsz is a multiple of 8 on this path)
 #pragma unroll
-      for (int u = 0; u < 8; ++u) xv[u] += mult * (r[u] * inv_s[(i + u) / gsz] * w[u]);
+      for (int u = 0; u < 8; ++u) xv[u] += mult * (r[u] * inv * w[u]);
       st8(row + i, xv);
       st8(x + (size_t)t * width + i, xv);
     }
@@ -383,8 +391,9 @@ __global__ void gated_gnorm_add_kernel(const Y* __restrict__ y, const E* __restr
       float w[8], o[8], r[8];
       ld8(w_next + i, w);
       ld8(row + i, r);
+      const float inv = inv_s[i / gsz];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) o[u] = r[u] * inv_s[(i + u) / gsz] * w[u];
+      for (int u = 0; u < 8; ++u) o[u] = r[u] * inv * w[u];
       st8(h + (size_t)t * width + i, o);
     }
     return;
@@ -393,7 +402,7 @@ __global__ void gated_gnorm_add_kernel(const Y* __restrict__ y, const E* __restr
     float v = to_f(y[(size_t)t * width + i]) + (bias ? to_f(bias[i]) : 0.f);
     if (gate) {
       const float z = to_f(gate[(size_t)t * gate_ld + i]) + (gate_bias ? to_f(gate_bias[i]) : 0.f);
-      v *= 1.f / (1.f + expf(-z));
+      v *= gate_logistic<E>(z);
     }
     row[i] = v;
   }
@@ -590,7 +599,7 @@ extern "C" int pk_res32_gated_gnorm_add(const void* y, int y_is_f32, const void*
   const size_t sm = gnorm_smem(width, groups);
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const int es = f32 ? 4 : 2;
-  const int vec = width % 8 == 0 && al16(y) && al16(bias) && al16(gate) && al16(gate_bias) && al16(w_post) && al16(x) && al16(w_next) && al16(h) &&
+  const int vec = (width / groups) % 8 == 0 && al16(y) && al16(bias) && al16(gate) && al16(gate_bias) && al16(w_post) && al16(x) && al16(w_next) && al16(h) &&
                   (gate_ld * es) % 16 == 0;
   const int thr = vec ? std::min(gnorm_threads(width, tokens), std::max(32, (width / 8 + 31) / 32 * 32)) : gnorm_threads(width, tokens);
   const dim3 g(tokens), b(thr);
