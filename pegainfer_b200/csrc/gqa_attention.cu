@@ -92,12 +92,13 @@ __device__ __forceinline__ float shape_score(float s, float softcap, float slope
   if (softcap > 0.f) s = softcap * tanhf(s / softcap);
   return s - slope * (float)distance;
 }
-// the same with tanh(z) = 1 - 2 / (e^(2z) + 1) on the fast exponential and division (absolute error of a few 1e-7: far below the
-// bf16 rounding of P in the tensor-core kernel, where every score of a tile pays for it)
-__device__ __forceinline__ float shape_score_fast(float s, float softcap, float inv_cap, float slope, int distance) {
-  if (softcap > 0.f) s = softcap * (1.f - __fdividef(2.f, __expf(2.f * s * inv_cap) + 1.f));
-  return s - slope * (float)distance;
+// 2^x on the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float fast_ex2(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
 }
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 constexpr int kGqaWarps = 8;
 constexpr int kGqaMaxPerLane = 8;  // features per lane: dim, vdim <= 256
@@ -222,7 +223,12 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
   const int ra = warp * 16 + gq, rb = ra + 8;
   const int req_a = s_req[ra], req_b = s_req[rb], pos_a = s_pos[ra], pos_b = s_pos[rb];
   const int lo_a = pos_a >= 0 ? first_visible(pos_a, chunk, x.window) : 0, lo_b = pos_b >= 0 ? first_visible(pos_b, chunk, x.window) : 0;
-  const float slope = head_slope(x.slope_log2, h, H), inv_cap = x.softcap > 0.f ? 1.f / x.softcap : 0.f;
+  // The tensor-core kernel keeps scores in units of log2 (every exponential is one ex2), and shapes a raw score q.k with
+  //   cap * tanh(z) = cap - 2 cap / (e^(2z) + 1),  z = q.k * scale / cap      (fast exponential and reciprocal: absolute error of a few
+  //   1e-7 of the cap, far below the bf16 rounding of P)
+  const bool capped = x.softcap > 0.f;
+  const float slope2 = head_slope(x.slope_log2, h, H) * kLog2e, cap2 = x.softcap * kLog2e;
+  const float c1 = capped ? 2.f * scale / x.softcap * kLog2e : scale * kLog2e;  // raw score -> ex2 argument of e^(2z) / -> plain scaled score
   const int split = blockIdx.z, nsplit = gridDim.z;  // few rows: every request's 64-key blocks are dealt out to gridDim.z CTAs
   // Q fragments (A operand, row-major 16 x DQ)
   uint32_t qa[DQ / 16][4];
@@ -297,15 +303,22 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
           mma_bf16_16816(s[np * 2], qa[kk], b[0], b[1]);
           mma_bf16_16816(s[np * 2 + 1], qa[kk], b[2], b[3]);
         }
+      // key j = k0 + 2 tq + c of this thread's column c is seen from a row at position p iff 0 <= p - j <= p - first_visible(p)
+      const int da = on_a ? pos_a - k0 - 2 * tq : -(1 << 20), db = on_b ? pos_b - k0 - 2 * tq : -(1 << 20);
+      const unsigned span_a = on_a ? pos_a - lo_a : 0, span_b = on_b ? pos_b - lo_b : 0;
+      const float fa = (float)da, fb = (float)db;
       float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
       for (int ni = 0; ni < kAmKeys / 8; ++ni)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int j = k0 + ni * 8 + 2 * tq + (e & 1);
+          const int c = ni * 8 + (e & 1);
           const bool top = e < 2;
-          const bool ok = top ? (on_a && j <= pos_a && j >= lo_a) : (on_b && j <= pos_b && j >= lo_b);
-          const float v = ok ? shape_score_fast(s[ni][e] * scale, x.softcap, inv_cap, slope, (top ? pos_a : pos_b) - j) : -INFINITY;
+          const bool ok = (unsigned)((top ? da : db) - c) <= (top ? span_a : span_b);
+          float v = s[ni][e] * c1;
+          if (capped) v = fmaf(-2.f * cap2, __fdividef(1.f, fast_ex2(fminf(v, 80.f)) + 1.f), cap2);
+          v = fmaf(-slope2, (top ? fa : fb) - (float)c, v);
+          v = ok ? v : -INFINITY;
           s[ni][e] = v;
           if (top) mx_a = fmaxf(mx_a, v);
           else mx_b = fmaxf(mx_b, v);
@@ -315,18 +328,20 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
       const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-      const float c_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), c_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+      // a row that has seen nothing yet keeps its maximum at -inf; subtracting 0 instead leaves its (all -inf) scores at 2^-inf = 0
+      const float sub_a = mn_a == -INFINITY ? 0.f : mn_a, sub_b = mn_b == -INFINITY ? 0.f : mn_b;
+      const float c_a = fast_ex2(m_a - sub_a), c_b = fast_ex2(m_b - sub_b);
       float sum_a = 0.f, sum_b = 0.f;
       uint32_t pa[kAmKeys / 16][4];
 #pragma unroll
       for (int ni = 0; ni < kAmKeys / 8; ++ni) {
-        const float e0 = mn_a == -INFINITY ? 0.f : expf(s[ni][0] - mn_a), e1 = mn_a == -INFINITY ? 0.f : expf(s[ni][1] - mn_a);
-        const float e2 = mn_b == -INFINITY ? 0.f : expf(s[ni][2] - mn_b), e3 = mn_b == -INFINITY ? 0.f : expf(s[ni][3] - mn_b);
-        const float r0 = round_bf16(e0), r1 = round_bf16(e1), r2 = round_bf16(e2), r3 = round_bf16(e3);
-        sum_a += r0 + r1;
-        sum_b += r2 + r3;
-        pa[ni >> 1][(ni & 1) * 2] = pack_bf16(r0, r1);
-        pa[ni >> 1][(ni & 1) * 2 + 1] = pack_bf16(r2, r3);
+        // P is rounded to bf16 once, for the second product; the row sum adds the rounded values
+        const uint32_t pk_a = pack_bf16(fast_ex2(s[ni][0] - sub_a), fast_ex2(s[ni][1] - sub_a));
+        const uint32_t pk_b = pack_bf16(fast_ex2(s[ni][2] - sub_b), fast_ex2(s[ni][3] - sub_b));
+        sum_a += bf16_lo(pk_a) + bf16_hi(pk_a);
+        sum_b += bf16_lo(pk_b) + bf16_hi(pk_b);
+        pa[ni >> 1][(ni & 1) * 2] = pk_a;
+        pa[ni >> 1][(ni & 1) * 2 + 1] = pk_b;
       }
       sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
       sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
@@ -358,8 +373,8 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
   }
   if (nsplit > 1) {  // partial state (running maximum, sum, unnormalised output) of this split; gqa_attention_merge_kernel finishes the rows
     const size_t sa = ((size_t)(h * nsplit + split) * T + (t0 + ra)), sb = ((size_t)(h * nsplit + split) * T + (t0 + rb));
-    if (req_a >= 0 && tq == 0) part_ml[sa * 2] = m_a, part_ml[sa * 2 + 1] = l_a;
-    if (req_b >= 0 && tq == 0) part_ml[sb * 2] = m_b, part_ml[sb * 2 + 1] = l_b;
+    if (req_a >= 0 && tq == 0) part_ml[sa * 2] = m_a * kLn2, part_ml[sa * 2 + 1] = l_a;  // maxima leave in natural units
+    if (req_b >= 0 && tq == 0) part_ml[sb * 2] = m_b * kLn2, part_ml[sb * 2 + 1] = l_b;
 #pragma unroll
     for (int ni = 0; ni < DV / 8; ++ni) {
       const int c = ni * 8 + 2 * tq;
@@ -368,10 +383,10 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
     }
     return;
   }
-  const float sk = sink ? bf2f(sink[h]) : -INFINITY;
+  const float sk = sink ? bf2f(sink[h]) * kLog2e : -INFINITY;  // the sink joins in the same log2 units
   const float mt_a = fmaxf(m_a, sk), mt_b = fmaxf(m_b, sk);
-  const float f_a = m_a == -INFINITY ? 0.f : expf(m_a - mt_a), f_b = m_b == -INFINITY ? 0.f : expf(m_b - mt_b);
-  const float d_a = l_a * f_a + (sink ? expf(sk - mt_a) : 0.f), d_b = l_b * f_b + (sink ? expf(sk - mt_b) : 0.f);
+  const float f_a = m_a == -INFINITY ? 0.f : exp2f(m_a - mt_a), f_b = m_b == -INFINITY ? 0.f : exp2f(m_b - mt_b);
+  const float d_a = l_a * f_a + (sink ? exp2f(sk - mt_a) : 0.f), d_b = l_b * f_b + (sink ? exp2f(sk - mt_b) : 0.f);
   const float i_a = f_a / d_a, i_b = f_b / d_b;
 #pragma unroll
   for (int ni = 0; ni < DV / 8; ++ni) {

@@ -80,32 +80,23 @@ struct ModelCfg {
 
 struct Lib {
   void* handle = nullptr;
-  // every design / only the sequential latent-attention block form / only the parallel block form
+  // every design / the block forms that route to experts / the ones with a dense feed-forward / one block form each
 #define PV_COMMON(X)                                                                                                                       \
   X(cuda_set_device) X(cublas_init) X(cublas_destroy) X(gemm_cuda) X(flashinfer_top1_cuda) X(pk_b200_set_pdl) X(pk_b200_launch_count)      \
   X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_proj_rows_f32out) X(pk_scale_to_f32) X(pk_top1_rows_f32)
 #define PV_MOE(X) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_moe_up_act) X(pk_moe_grouped_act)
+#define PV_DENSE(X) X(pk_act) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
 #define PV_BLOCK0(X)                                                                                                                        \
-  X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_act) X(pk_rope_slice) X(pk_latent_kv_append)             \
-  X(pk_latent_attention) X(pk_router_grouped_topk) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
+  X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_rope_slice) X(pk_latent_kv_append) X(pk_latent_attention) \
+  X(pk_router_grouped_topk)
 #define PV_BLOCK1(X)                                                                                                                        \
   X(pk_res32_embed_scaled) X(pk_res32_add_dyt) X(pk_res32_dyt_rows) X(pk_gqa_rope_append) X(pk_gqa_attention) X(pk_causal_conv_silu)       \
   X(pk_gated_delta_seq) X(pk_mlstm_seq) X(pk_head_norm_gate) X(pk_router_topk_ex)
 #define PV_BLOCK2(X)                                                                                                                        \
   X(pk_res32_embed_gnorm) X(pk_res32_gated_gnorm_add) X(pk_res32_gnorm_rows) X(pk_gqa_rope_append_ex) X(pk_gqa_attention_ex) X(pk_rope_slice_ex)   \
-  X(pk_latent_kv_append_ex) X(pk_latent_attention_ex) X(pk_act) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu) X(pk_b200_gemm_segments)
+  X(pk_latent_kv_append_ex) X(pk_latent_attention_ex) X(pk_b200_gemm_segments)
 #define PV_FN(name) decltype(&::name) name = nullptr;
-  PV_COMMON(PV_FN) PV_MOE(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN)
-  // block 2 shares pk_act / pk_b200_gemv_fused / pk_b200_gemm_swiglu with block 0
-  decltype(&::pk_res32_embed_gnorm) pk_res32_embed_gnorm = nullptr;
-  decltype(&::pk_res32_gated_gnorm_add) pk_res32_gated_gnorm_add = nullptr;
-  decltype(&::pk_res32_gnorm_rows) pk_res32_gnorm_rows = nullptr;
-  decltype(&::pk_gqa_rope_append_ex) pk_gqa_rope_append_ex = nullptr;
-  decltype(&::pk_gqa_attention_ex) pk_gqa_attention_ex = nullptr;
-  decltype(&::pk_rope_slice_ex) pk_rope_slice_ex = nullptr;
-  decltype(&::pk_latent_kv_append_ex) pk_latent_kv_append_ex = nullptr;
-  decltype(&::pk_latent_attention_ex) pk_latent_attention_ex = nullptr;
-  decltype(&::pk_b200_gemm_segments) pk_b200_gemm_segments = nullptr;
+  PV_COMMON(PV_FN) PV_MOE(PV_FN) PV_DENSE(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN) PV_BLOCK2(PV_FN)
 #undef PV_FN
   // a library built for one design need not hold the other block form's kernels: only what `block_kind` runs is required
   std::string load(const std::string& p, int block_kind) {
@@ -117,11 +108,11 @@ struct Lib {
   if (!name) missing += std::string(" ") + #name;
     PV_COMMON(PV_REQ)
     if (block_kind == 0) {
-      PV_MOE(PV_REQ) PV_BLOCK0(PV_REQ)
+      PV_MOE(PV_REQ) PV_DENSE(PV_REQ) PV_BLOCK0(PV_REQ)
     } else if (block_kind == 1) {
       PV_MOE(PV_REQ) PV_BLOCK1(PV_REQ)
     } else {  // the sandwich block form has no mixture of experts
-      PV_BLOCK2(PV_REQ)
+      PV_DENSE(PV_REQ) PV_BLOCK2(PV_REQ)
     }
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
