@@ -721,9 +721,11 @@ def test_rejected_step_leaves_lengths_and_pages_untouched():
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_long_decoding_and_captured_steps(dtype):
     """a 300-token prompt and 260 decoded tokens (captured launch sequences from the second step of a kind on, across a graph bucket
-    border at 512; windows of 100 and 130 tokens leave the prompt behind while decoding) against the same steps run eagerly and
-    against the oracle"""
-    cfg = model_cfg([(attn(4, 2, 32, 32, 100), 32), (latent(2, 32, 16, 32, 64, 130), 0), (attn(2, 1, 24, 40, 0), 48)], vocab=96, width=64)
+    border at 512; windows of 100 and 130 tokens leave the prompt behind while decoding; two layers without a window, one of them on
+    the tensor-core kernel in bf16, whose key split then follows the step's longest context) against the same steps run eagerly
+    and against the oracle"""
+    cfg = model_cfg([(attn(4, 2, 32, 32, 100), 32), (latent(2, 32, 16, 32, 64, 130), 0), (attn(2, 1, 24, 40, 0), 48), (attn(2, 2, 64, 64, 0, cap=0.0), 0)],
+                    vocab=96, width=64)
     w = make_weights(cfg, 26, SHARP[dtype])
     toks = tokens_for(cfg, 560, 6)
     outs = []
