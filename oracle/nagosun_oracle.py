@@ -38,7 +38,7 @@ def unit_rms(x, eps: float):
 
 
 def visible(pos_q, pos_k, window: int):
-    """[queries, keys] bool: key j is seen from query i when 0 <= i - j < window (window 0: any distance back)."""
+    """[queries, keys] bool: a key is seen when it lies d positions behind the query with 0 <= d < window (window 0: any d >= 0)."""
     d = pos_q[:, None] - pos_k[None, :]
     ok = d >= 0
     if window:
@@ -55,7 +55,8 @@ def soft_cap(s, cap: float):
 
 
 def softmax_plus_one(s, ok):
-    """p_j = exp(s_j) / (1 + sum over visible j of exp(s_j)): a sink with score 0 and no value."""
+    """weights e^{s_k} / (1 + sum of e^{s_k'} over the visible keys k'): the softmax over the keys plus one slot of score zero that
+    carries no value (computed with the usual shift by the largest score, the extra slot included)."""
     m = torch.where(ok, s, torch.full_like(s, -float("inf"))).max(-1, keepdim=True).values.clamp(min=0.0)
     e = torch.where(ok, torch.exp(s - m), torch.zeros_like(s))
     return e / (torch.exp(-m) + e.sum(-1, keepdim=True))

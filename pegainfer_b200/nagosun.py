@@ -8,7 +8,7 @@ norms on an fp32 residual stream, its result is gated by a logistic projection o
 where ``gn`` splits a row into ``norm.groups`` equal consecutive parts and divides each by its own root mean square.  The
 embedding and the last hidden state pass the same norm; the logits carry a multiplier.  Two mixers:
 
-* ``attention`` -- grouped-query attention with projection biases and no rotary embedding: positions enter through a linear
+* ``attention`` -- grouped-query attention with projection biases and no rotary embedding: the only position signal is a linear
   distance bias (head ``h`` of ``H`` subtracts ``2^(-8 (h + 1) / H)`` times the distance from the score).  The scaled score is
   soft-capped (``cap * tanh(s / cap)``) before the bias; a sliding window limits the visible keys; the softmax denominator
   carries a sink of score zero (one is added to it); cached values are unit-RMS per head; the concatenated heads are multiplied
