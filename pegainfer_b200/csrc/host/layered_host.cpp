@@ -221,7 +221,7 @@ struct Model {
   bool put_uk(Layer& L, const void* data, const std::string& name, int rows, int cols);
   bool run_experts(Layer& L, int T, const void* shared);
   bool run_parallel_layer(int li, int T, const int* M, int n);
-  bool run_sandwich_layer(int li, int T, int max_kv, const int* M, int n);
+  bool run_sandwich_layer(int li, int T, int max_kv, const int* M);
   bool lin_segments(const Mat& W, const void* X, void* const* Y, const int* seg_rows, int N);
   bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
   bool forward(int T, int n, int n_rows, int max_kv, int want_sample);
@@ -876,7 +876,7 @@ bool Model::lin_segments(const Mat& W, const void* X, void* const* Y, const int*
 
 // Sandwich block: on entry xa holds gnorm(x, norm1) of this layer; on exit x holds the layer's result and xa the next layer's
 // pre-norm (nothing after the last layer).
-bool Model::run_sandwich_layer(int li, int T, int max_kv, const int* M, int n) {
+bool Model::run_sandwich_layer(int li, int T, int max_kv, const int* M) {
   Layer& L = layers[li];
   const LayerCfg& a = L.c;
   const int W = c.width, f32 = c.f32, H = a.heads, G = a.kv_heads, mk = a.mixer_kind, rg = c.gated_residual ? W : 0;
@@ -994,7 +994,7 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
             "embedding"))
       return false;
     for (int li = 0; li < c.n_layers; ++li)
-      if (!run_sandwich_layer(li, T, max_kv, M, n)) return false;
+      if (!run_sandwich_layer(li, T, max_kv, M)) return false;
   } else {
     if (!rc(k.pk_res32_embed_scaled(embed.d.ptr, d_tok, (float*)x.ptr, W, T, c.embed_scale, c.f32, st), "embedding")) return false;
     // every layer's residual sum is folded into the next layer's norm (the last one into a plain sum)
