@@ -503,7 +503,8 @@ int pk_gated_delta_seq(const void* qkv, int ld, int q_off, int k_off, int v_off,
 int pk_mlstm_seq(const void* qkv, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, int forget_off, int input_off,
                  const float* input_bias, const float* forget_bias, float cap, float* state, long slot_stride, const int* slot, const int* row0,
                  const int* len, float* out, float* den, int heads, int dim, int vdim, int entries, int f32, pk_stream st);
-/* out[t,h,:] = rms_norm(o[t,h,:] / den[t,h]) * w[h * w_stride + :] * act(gate[t, gate_off + h*vdim + :]); act 0 silu, 1 logistic; den may be NULL */
+/* out[t,h,:] = rms_norm(o[t,h,:] / den[t,h]) * w[h * w_stride + :] * act(gate[t, gate_off + h*vdim + :]); act 0 silu, 1 logistic; den may be NULL.
+ * act 2: the silu gate comes first, out = rms_norm(o * silu(gate)) * w ("heads" may then be any equal parts of the row: norm groups). */
 int pk_head_norm_gate(const float* o, const float* den, const void* w, int w_stride, const void* gate, int ld_gate, int gate_off, void* out, int tokens,
                       int heads, int vdim, float eps, int act, int f32, pk_stream st);
 /* Router with options (moe.cu): logits rows of stride ld; score_kind 0 softmax / 1 logistic; correction (may be NULL) added for the choice only;
@@ -541,6 +542,7 @@ typedef struct pk_attn_extra {
   const void* gate;  /* element type, rows of stride gate_ld: out[t, h, d] *= logistic(gate[t * gate_ld + h * vdim + d]) */
   long gate_ld;
   int max_kv_len;    /* longest context in the step (0 = unknown): lets a step of few rows split the key axis over CTAs */
+  int keep_first;    /* with a window: the first keep_first positions of the sequence stay visible to every later query */
 } pk_attn_extra;
 /* pk_gqa_attention with those options (extra == NULL: none).  A sink of score zero ("one added to the denominator") is a sink vector of zeros. */
 int pk_gqa_attention_ex(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
@@ -558,6 +560,56 @@ int pk_latent_kv_append_ex(const void* dkv, const void* norm_w, const int* posit
 int pk_latent_attention_ex(const void* qa, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                            const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
                            int window, int max_kv_len, int f32, pk_stream st);
+
+/* =============== pre-norm blocks, normed queries / keys, kept-first windows, state-space layers, clamped gated experts ===============
+ * rms(v)[i] = v[i] / sqrt(mean(v^2) + eps).  A pre-norm block feeds h = rms(x) * w to a sublayer and adds the sublayer's result to x. */
+/* x[t] = embed[ids[t]] * scale;  h[t] = rms(x[t]) * w_next in the element type (w_next NULL: no h); h32 (may be NULL) gets h unrounded */
+int pk_res32_embed_scaled_norm(const void* embed, const int* token_ids, float scale, float* x, const void* w_next, void* h, float* h32, int width,
+                               float eps, int tokens, int f32, pk_stream st);
+/* x[t] += mult * (branch(ya[t], wa) + branch(yb[t], wb)), branch(y, w) = w ? rms(y) * w : y;  then h / h32 as above.  ya: element type, or float when
+ * ya_is_f32; yb: element type.  ya, yb, wa, wb may each be NULL (no such branch / branch not normed).  -2: row too wide for shared memory. */
+int pk_res32_branches_add_norm(const void* ya, int ya_is_f32, const void* wa, const void* yb, const void* wb, float mult, float* x, const void* w_next,
+                               void* h, float* h32, int width, float eps, int tokens, int f32, pk_stream st);
+/* out = cap * tanh(float(in) * scale / cap); cap 0: float(in) * scale */
+int pk_logits_scale_cap(const void* in, int in_f32, float* out, long n, float scale, float cap, pk_stream st);
+/* in [tokens, 2F] = [gate | up]:  g = min(gate, limit), u = clamp(up, -limit, limit), out[t][f] = g * logistic(slope * g) * (u + 1) */
+int pk_act_clamped(const void* in, void* out, int F, int tokens, float limit, float slope, int f32, pk_stream st);
+/* What pk_gqa_norm_append does to q and k before they are cached / handed to the attention. */
+typedef struct pk_qk_prep {
+  int norm_kind;         /* 0 none; 1 RMS norm per head, weights [dim] shared by the heads; 2 one RMS norm over the whole projection, weights [heads*dim] / [kv_heads*dim] */
+  const void* q_weight;  /* element type */
+  const void* k_weight;
+  float eps;
+  float temp_coef;       /* q *= 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position p; temp_every 0: no factor */
+  int temp_every;
+  int values_are_keys;   /* 1: qkv has no v part; the cached values are the keys as projected, before their norm (vdim == dim) */
+} pk_qk_prep;
+/* pk_gqa_rope_append without biases and with those steps: norm, then rotation of the first `dims` entries, then the query's factor. */
+int pk_gqa_norm_append(const void* qkv, int ld, const int* positions, const int* req, const int* page_off, const int* pages, void* q_out, void* cache,
+                       long page_stride, int page_size, int heads, int kv_heads, int dim, int vdim, int dims, int interleaved, const float* freq,
+                       float mag, const pk_qk_prep* prep, int tokens, int f32, pk_stream st);
+/* pk_causal_conv_silu with a per-channel bias inside the activation (bias NULL: none) */
+int pk_causal_conv_silu_bias(const void* in, int ld_in, const void* w, const void* bias, float* state, long slot_stride, const int* req, const int* slot,
+                             const int* row0, const int* len, void* out, int ld_out, int channels, int taps, int tokens, int entries, int f32,
+                             pk_stream st);
+/* State-space duality over each entry's rows: per head h (group h / (heads / groups)), step = softplus(dt[t, dt_off + h] + dt_bias[h]),
+ * S <- exp(-exp(a_log[h]) * step) S + step * B_t x_t^T,  out[t, h] = S^T C_t + d_skip[h] * x_t.  xbc [tokens, ld]: x (heads x vdim) at x_off,
+ * B and C (groups x state_dim) at b_off / c_off; dt [tokens, ld_dt] in the element type.  State S [heads][state_dim][vdim] fp32 per slot. */
+int pk_ssd_seq(const void* xbc, int ld, int x_off, int b_off, int c_off, const void* dt, int ld_dt, int dt_off, const float* a_log, const float* dt_bias,
+               const float* d_skip, float* state, long slot_stride, const int* slot, const int* row0, const int* len, float* out, int heads, int groups,
+               int state_dim, int vdim, int entries, int f32, pk_stream st);
+/* Router over raw logits: score = logits + bias (bias may be NULL); the `top` largest scores win (lowest index on ties), weights = softmax over the
+ * winners' scores alone, times scale. */
+int pk_router_topk_logits(const float* logits, int ld, const float* bias, int* ids, float* weights, int tokens, int experts, int top, float scale,
+                          pk_stream st);
+/* pk_moe_up_act / pk_moe_grouped_act with activation parameters.  act 2: gated with clamped pre-activations, rows interleaved as for act 1:
+ * g = min(gate, p0), u = clamp(up, -p0, p0), hid = g * logistic(p1 * g) * (u + 1).  With a shared expert and shared_gate == NULL (here and in
+ * pk_moe_down_combine) the shared expert's output is added without a gate. */
+int pk_moe_up_act_p(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int act, float p0, float p1,
+                    int f32, pk_stream st);
+int pk_moe_grouped_act_p(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                         const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act, float p0,
+                         float p1, pk_stream st);
 
 #ifdef __cplusplus
 }

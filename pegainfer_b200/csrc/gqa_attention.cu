@@ -6,6 +6,10 @@
 // Further options (pk_attn_extra): a sliding window (keys p - window + 1 .. p), a soft cap on the scaled score
 // (cap * tanh(score / cap)), a linear distance bias (head h subtracts 2^(-slope_log2 (h + 1) / heads) * (p - j)), an
 // element-wise logistic gate on the output, and -- in the append -- an unweighted RMS norm of every cached value head.
+// A window may keep the first `keep_first` positions of the sequence visible for good (they keep their true positions).
+// gqa_norm_append_kernel is the append for designs that norm q and k (per head with one weight for all heads, or over the whole
+// projection at once) before rotating them, stretch the query by a factor that grows with the logarithm of the position, or
+// cache the keys as projected in the place of values.
 //
 // Cache: token at position p of a request lives in page pages[page_off[req] + p / page_size], slot p % page_size, at
 //   cache + page * page_stride + slot * (G * dim + G * vdim):  [K of G heads | V of G heads].
@@ -73,6 +77,87 @@ __global__ void gqa_rope_append_kernel(const E* __restrict__ qkv, int ld, const 
   }
 }
 
+// Append for designs that norm q and k before they rotate.  qkv [tokens, ld] = [q (H*dim) | k (G*dim) | v (G*vdim)]; with `v_from_k` there
+// is no v part and the cached values are the keys as projected (vdim == dim).  norm_kind 1: every head of q (of k) is divided by its own
+// root mean square and multiplied by qw (kw) [dim], one weight for all heads; 2: the whole q row (k row) is divided by ONE root mean
+// square and multiplied by qw [H*dim] (kw [G*dim]); 0: no norm.  Then the first `dims` entries of every head rotate, and q is
+// multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every 0: not).  One CTA per token; the row lives in shared
+// memory as fp32; sums of squares are added per head by one warp and then in head order, so a row's result does not depend on timing.
+template <typename E>
+__global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const int* __restrict__ pos, const int* __restrict__ req,
+                                       const int* __restrict__ page_off, const int* __restrict__ pages, E* __restrict__ q_out, E* __restrict__ cache,
+                                       long page_stride, int page_size, int H, int G, int dim, int vdim, int dims, int interleaved,
+                                       const float* __restrict__ freq, float mag, const E* __restrict__ qw, const E* __restrict__ kw, int norm_kind,
+                                       float eps, float temp_coef, int temp_every, int v_from_k) {
+  extern __shared__ float na_sm[];
+  float* row = na_sm;             // [nq + nk]
+  float* inv = row + (H + G) * dim;  // [H + G] reciprocal root mean square per head
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, p = pos[t], lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const E* src = qkv + (size_t)t * ld;
+  const int nq = H * dim, nk = G * dim, nv = G * vdim, half = dims >> 1;
+  E* slot = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (nk + nv);
+  for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) row[e] = to_f(src[e]);
+  if (v_from_k) {
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) slot[nk + e] = src[nq + e];
+  } else {
+    for (int e = threadIdx.x; e < nv; e += blockDim.x) slot[nk + e] = src[nq + nk + e];
+  }
+  __syncthreads();
+  if (norm_kind) {
+    for (int hd = warp; hd < H + G; hd += nw) {
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) ss = fmaf(row[hd * dim + d], row[hd * dim + d], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) inv[hd] = ss;
+    }
+    __syncthreads();
+    if (norm_kind == 1) {
+      if (threadIdx.x < H + G) inv[threadIdx.x] = 1.f / sqrtf(inv[threadIdx.x] / (float)dim + eps);
+      __syncthreads();
+    } else {
+      float sq = 0.f, sk = 0.f;
+      for (int hd = 0; hd < H; ++hd) sq += inv[hd];
+      for (int hd = 0; hd < G; ++hd) sk += inv[H + hd];
+      __syncthreads();
+      const float iq = 1.f / sqrtf(sq / (float)nq + eps), ik = 1.f / sqrtf(sk / (float)nk + eps);
+      for (int hd = threadIdx.x; hd < H + G; hd += blockDim.x) inv[hd] = hd < H ? iq : ik;
+      __syncthreads();
+    }
+    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+      const bool is_q = e < nq;
+      const int el = is_q ? e : e - nq;
+      const E* w = is_q ? qw : kw;
+      row[e] *= inv[e / dim] * to_f(w[norm_kind == 1 ? el % dim : el]);
+    }
+    __syncthreads();
+  }
+  const float stretch = temp_every > 0 ? 1.f + temp_coef * logf((float)((p + 1) / temp_every) + 1.f) : 1.f;
+  for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+    float v = row[e];
+    const int d = e % dim;
+    if (d < dims) {
+      int i, pe;
+      bool first;
+      if (interleaved) {
+        i = d >> 1;
+        first = (d & 1) == 0;
+        pe = first ? e + 1 : e - 1;
+      } else {
+        first = d < half;
+        i = first ? d : d - half;
+        pe = first ? e + half : e - half;
+      }
+      const float a = (float)p * freq[i];
+      const float c = cosf(a) * mag, sn = sinf(a) * mag;
+      v = first ? v * c - row[pe] * sn : v * c + row[pe] * sn;
+    }
+    if (e < nq) q_out[(size_t)t * nq + e] = from_f<E>(v * stretch);
+    else slot[e - nq] = from_f<E>(v);
+  }
+}
+
 // the options of pk_attn_extra as the kernels take them (all off when zero / null)
 struct AttnExtra {
   int window;
@@ -80,6 +165,7 @@ struct AttnExtra {
   const void* gate;
   long gate_ld;
   int max_kv_len;
+  int keep_first;
 };
 __device__ __forceinline__ int first_visible(int p, int chunk, int window) {
   int lo = chunk > 0 ? (p / chunk) * chunk : 0;
@@ -126,10 +212,13 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  // two keys per trip (j and j + warps): their loads, dot products and exponentials overlap, which halves the dependent chain per key
-  for (int j = lo + warp; j <= p; j += 2 * kGqaWarps) {
-    const int j2 = j + kGqaWarps;
-    const bool two = j2 <= p;
+  // visible keys: the first `nf` positions (kept for good, when the window has left them behind), then lo .. p
+  const int nf = min(x.keep_first, lo), n_vis = nf + p - lo + 1;
+  // two keys per trip (i and i + warps): their loads, dot products and exponentials overlap, which halves the dependent chain per key
+  for (int i = warp; i < n_vis; i += 2 * kGqaWarps) {
+    const int i2 = i + kGqaWarps;
+    const bool two = i2 < n_vis;
+    const int j = i < nf ? i : lo + (i - nf), j2 = i2 < nf ? i2 : lo + (i2 - nf);
     const E* kv_a = cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok;
     const E* kv_b = two ? cache + (size_t)pg[j2 / page_size] * page_stride + (size_t)(j2 % page_size) * tok : kv_a;
     float ka[kGqaMaxPerLane], kb[kGqaMaxPerLane], va[kGqaMaxPerLane], vb[kGqaMaxPerLane];
@@ -253,13 +342,13 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
     const int p_min = s_pos[r_first], p_max = s_pos[r_last];
     const int k_lo = first_visible(p_min, chunk, x.window);
     const int* pg = pages + page_off[rq];
-    // stage `buf` <- keys k0 .. k0 + 63 of this request (cp.async; rows outside [k_lo, p_max] are zero-filled)
+    // stage `buf` <- keys k0 .. k0 + 63 of this request (cp.async; rows outside [k_lo, p_max] and not among the kept first are zero-filled)
     auto load = [&](int k0, int buf) {
       bf16* Kd = Ks0 + buf * kAmKeys * LDK;
       bf16* Vd = Vs0 + buf * kAmKeys * LDV;
       if (tid < kAmKeys) {  // one page-table read per key row, not one per 16-byte piece
         const int j = k0 + tid;
-        s_slot[buf][tid] = (j <= p_max && j >= k_lo) ? (long long)pg[j / page_size] * page_stride + (long long)(j % page_size) * tok : -1;
+        s_slot[buf][tid] = (j <= p_max && (j >= k_lo || j < x.keep_first)) ? (long long)pg[j / page_size] * page_stride + (long long)(j % page_size) * tok : -1;
       }
       __syncthreads();
 #pragma unroll 4
@@ -278,16 +367,19 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
       }
       cp_async_commit();
     };
+    // blocks to walk: those that hold kept first keys and lie wholly before the window's first block, then the window's blocks
     const int k_start = k_lo - (k_lo % kAmKeys);
-    const int n_blocks = (p_max - k_start) / kAmKeys + 1, per_split = (n_blocks + nsplit - 1) / nsplit;
-    const int k_first = k_start + split * per_split * kAmKeys, k_last = min(p_max, k_first + per_split * kAmKeys - 1);
+    const int n_kept = min((x.keep_first + kAmKeys - 1) / kAmKeys, k_start / kAmKeys);
+    const int n_blocks = n_kept + (p_max - k_start) / kAmKeys + 1, per_split = (n_blocks + nsplit - 1) / nsplit;
+    const int b_first = split * per_split, b_end = min(n_blocks, b_first + per_split);
+    auto block_k0 = [&](int b) { return b < n_kept ? b * kAmKeys : k_start + (b - n_kept) * kAmKeys; };
     __syncthreads();  // the previous request's readers are done with both stages
-    if (k_first <= k_last) load(k_first, 0);
-    for (int k0 = k_first, it = 0; k0 <= k_last; k0 += kAmKeys, ++it) {
-      const int buf = it & 1;
+    if (b_first < b_end) load(block_k0(b_first), 0);
+    for (int b = b_first, it = 0; b < b_end; ++b, ++it) {
+      const int buf = it & 1, k0 = block_k0(b);
       cp_async_wait_all();
       __syncthreads();  // this block has landed, and nobody reads the other stage any more
-      if (k0 + kAmKeys <= k_last) load(k0 + kAmKeys, buf ^ 1);  // overlaps the products below
+      if (b + 1 < b_end) load(block_k0(b + 1), buf ^ 1);  // overlaps the products below
       const bf16* Ks = Ks0 + buf * kAmKeys * LDK;
       const bf16* Vs = Vs0 + buf * kAmKeys * LDV;
       const bool on_a = req_a == rq, on_b = req_b == rq;
@@ -307,6 +399,7 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
       const int da = on_a ? pos_a - k0 - 2 * tq : -(1 << 20), db = on_b ? pos_b - k0 - 2 * tq : -(1 << 20);
       const unsigned span_a = on_a ? pos_a - lo_a : 0, span_b = on_b ? pos_b - lo_b : 0;
       const float fa = (float)da, fb = (float)db;
+      const int kept = x.keep_first - k0 - 2 * tq;  // column c holds one of the kept first keys iff c < kept
       float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
       for (int ni = 0; ni < kAmKeys / 8; ++ni)
@@ -314,7 +407,8 @@ __global__ void __launch_bounds__(128, 3) gqa_attention_mma_kernel(const bf16* _
         for (int e = 0; e < 4; ++e) {
           const int c = ni * 8 + (e & 1);
           const bool top = e < 2;
-          const bool ok = (unsigned)((top ? da : db) - c) <= (top ? span_a : span_b);
+          const int dist = (top ? da : db) - c;
+          const bool ok = (unsigned)dist <= (top ? span_a : span_b) || (c < kept && dist >= 0);
           float v = s[ni][e] * c1;
           if (capped) v = fmaf(-2.f * cap2, __fdividef(1.f, fast_ex2(fminf(v, 80.f)) + 1.f), cap2);
           v = fmaf(-slope2, (top ? fa : fb) - (float)c, v);
@@ -457,7 +551,7 @@ static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, c
   // row can see is bounded by the window / chunk, else by the longest context of the step (when the caller knows it).
   const int tiles = (T + kAmRows - 1) / kAmRows;
   int span = x.max_kv_len;
-  if (x.window > 0) span = span > 0 ? min(span, x.window + T) : x.window + T;
+  if (x.window > 0) span = span > 0 ? min(span, x.window + x.keep_first + T) : x.window + x.keep_first + T;
   if (chunk > 0) span = span > 0 ? min(span, chunk) : chunk;
   int splits = 1;
   ThreadState& ts = tls();
@@ -504,6 +598,30 @@ extern "C" int pk_gqa_rope_append_ex(const void* qkv, int ld, const void* bias, 
   return (int)cudaGetLastError();
 }
 
+extern "C" int pk_gqa_norm_append(const void* qkv, int ld, const int* positions, const int* req, const int* page_off, const int* pages, void* q_out,
+                                  void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim, int vdim, int dims, int interleaved,
+                                  const float* freq, float mag, const pk_qk_prep* prep, int tokens, int f32, pk_stream st) {
+  if (!qkv || !positions || !req || !page_off || !pages || !q_out || !cache || !prep || tokens <= 0 || heads <= 0 || kv_heads <= 0 ||
+      heads % kv_heads || dim <= 0 || vdim <= 0 || dims < 0 || dims > dim || (dims & 1) || (dims > 0 && !freq) || page_size <= 0 ||
+      prep->norm_kind < 0 || prep->norm_kind > 2 || (prep->norm_kind && (!prep->q_weight || !prep->k_weight)) || prep->temp_every < 0 ||
+      (prep->values_are_keys && vdim != dim))
+    return -1;
+  const size_t smem = ((size_t)(heads + kv_heads) * dim + heads + kv_heads) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  const int threads = tokens > 64 ? 256 : std::min(1024, std::max(128, ((heads + kv_heads) * dim / 2 + 31) / 32 * 32));
+#define PK_NA(E)                                                                                                                                   \
+  do {                                                                                                                                             \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gqa_norm_append_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);                \
+    launch(gqa_norm_append_kernel<E>, dim3(tokens), dim3(threads), smem, st, true, (const E*)qkv, ld, positions, req, page_off, pages, (E*)q_out,  \
+           (E*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag, (const E*)prep->q_weight,                  \
+           (const E*)prep->k_weight, prep->norm_kind, prep->eps, prep->temp_coef, prep->temp_every, prep->values_are_keys);                        \
+  } while (0)
+  if (f32) PK_NA(float);
+  else PK_NA(bf16);
+#undef PK_NA
+  return (int)cudaGetLastError();
+}
+
 extern "C" int pk_gqa_attention(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                                 const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim,
                                 int vdim, float scale, int chunk, int f32, pk_stream st) {
@@ -517,10 +635,10 @@ extern "C" int pk_gqa_attention_ex(const void* q, const void* cache, const void*
   if (!q || !cache || !positions || !req || !page_off || !pages || !out || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       dim <= 0 || vdim <= 0 || chunk < 0 || page_size <= 0)
     return -1;
-  AttnExtra x{0, 0.f, 0.f, nullptr, 0, 0};
+  AttnExtra x{0, 0.f, 0.f, nullptr, 0, 0, 0};
   if (extra) {
-    if (extra->window < 0 || extra->softcap < 0.f || extra->slope_log2 < 0.f || extra->max_kv_len < 0) return -1;
-    x = AttnExtra{extra->window, extra->softcap, extra->slope_log2, extra->gate, extra->gate_ld, extra->max_kv_len};
+    if (extra->window < 0 || extra->softcap < 0.f || extra->slope_log2 < 0.f || extra->max_kv_len < 0 || extra->keep_first < 0) return -1;
+    x = AttnExtra{extra->window, extra->softcap, extra->slope_log2, extra->gate, extra->gate_ld, extra->max_kv_len, extra->window > 0 ? extra->keep_first : 0};
   }
   if (dim > 32 * kGqaMaxPerLane || vdim > 32 * kGqaMaxPerLane) return -2;
   const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&

@@ -8,7 +8,9 @@
 //   Variants (parameters of the `_ex` / `_act` entry points): logistic scores instead of softmax, a per-expert correction added to
 //   the scores for the CHOICE only (weights use the uncorrected score), a group scoring as the sum of its two best corrected
 //   scores, weights not renormalised; experts with a gated activation, hid = silu(W_gate x) * (W_up x), whose gate and up rows
-//   are stored interleaved (row 2f = gate f, row 2f + 1 = up f) so that one pass yields both.
+//   are stored interleaved (row 2f = gate f, row 2f + 1 = up f) so that one pass yields both; a gated activation with clamped
+//   pre-activations, g = min(gate, limit), u = clamp(up, -limit, limit), hid = g * logistic(slope * g) * (u + 1); a router that picks
+//   the largest logits (+ bias) and weighs the picked experts by the softmax over their logits alone; a shared expert without a gate.
 // The per-token form reads only the chosen experts' weights: the decode path (a few tokens) is bound by those bytes.
 #include "common.cuh"
 #include "typed.cuh"
@@ -30,6 +32,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 // one warp per token; shared memory: scores [E] + group eligibility [groups]
 // score_kind 0: softmax over the experts, 1: logistic per expert.  corr (may be null): added to the score for choosing.
+// score_kind 2: the score is the logit + corr (a bias that counts for choice AND weight); weights = softmax over the chosen scores.
 // group_top 1: a group scores as its best expert, 2: as the sum of its two best.  renorm 1: weights divided by their sum.
 __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int* __restrict__ ids,
                                            float* __restrict__ wts, int E, int top, int groups, int keep, float scale, int score_kind, int group_top,
@@ -57,11 +60,13 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int ldz,
     const float inv = 1.f / sum;
     __syncwarp();
     for (int e = lane; e < E; e += 32) s[e] *= inv;
-  } else {
+  } else if (score_kind == 1) {
     for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-zr[e]));
+  } else {
+    for (int e = lane; e < E; e += 32) s[e] = zr[e] + (corr ? corr[e] : 0.f);
   }
   __syncwarp();
-  for (int e = lane; e < E; e += 32) c[e] = s[e] + (corr ? corr[e] : 0.f);
+  for (int e = lane; e < E; e += 32) c[e] = score_kind == 2 ? s[e] : s[e] + (corr ? corr[e] : 0.f);
   __syncwarp();
   const int per = E / groups;
   for (int g = lane; g < groups; g += 32) {
@@ -110,6 +115,15 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int ldz,
     }
     __syncwarp();
   }
+  __syncwarp();
+  if (score_kind == 2) {  // the first pick carries the largest score
+    const float mx = wts[(size_t)t * top];
+    float sum = 0.f;
+    for (int r = lane; r < top; r += 32) sum += expf(wts[(size_t)t * top + r] - mx);
+    sum = warp_sum(sum);
+    for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = expf(wts[(size_t)t * top + r] - mx) / sum * scale;
+    return;
+  }
   const float f = renorm ? scale / (total + 1e-20f) : scale;
   for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] *= f;
 }
@@ -118,10 +132,11 @@ constexpr int kMoeDownRowsPerBlock = 8;  // one output row per warp: each row al
 constexpr int kMoeRowsPerBlock = 32;  // weight rows per CTA: a decode step spreads one expert over many SMs
 
 // hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]).  GATED 0: act = relu^2, W_up [experts, ff, width].  GATED 1: W_up [experts, 2 ff, width] with
-// row 2f = gate f and row 2f + 1 = up f; hid = silu(gate . x) * (up . x).  Grid (token, choice, slice of ff rows).
+// row 2f = gate f and row 2f + 1 = up f; hid = silu(gate . x) * (up . x).  GATED 2: the same rows, g = min(gate . x, p0), u = clamp(up . x,
+// -p0, p0), hid = g * logistic(p1 * g) * (u + 1).  Grid (token, choice, slice of ff rows).
 template <typename E, int GATED>
 __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_up, const int* __restrict__ ids, E* __restrict__ hid, int width,
-                              int ff) {
+                              int ff, float p0, float p1) {
   extern __shared__ __align__(16) float xs[];
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
@@ -134,8 +149,14 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
   for (int f = blockIdx.z * kMoeRowsPerBlock + warp; f < f_end; f += nw) {
     float r;
     if (GATED) {
-      const float g = warp_dot(W + (size_t)(2 * f) * width, xs, width, lane), u = warp_dot(W + (size_t)(2 * f + 1) * width, xs, width, lane);
-      r = g / (1.f + expf(-g)) * u;
+      float g = warp_dot(W + (size_t)(2 * f) * width, xs, width, lane), u = warp_dot(W + (size_t)(2 * f + 1) * width, xs, width, lane);
+      if (GATED == 2) {
+        g = fminf(g, p0);
+        u = fminf(fmaxf(u, -p0), p0);
+        r = g / (1.f + expf(-p1 * g)) * (u + 1.f);
+      } else {
+        r = g / (1.f + expf(-g)) * u;
+      }
     } else {
       const float u = fmaxf(warp_dot(W + (size_t)f * width, xs, width, lane), 0.f);
       r = u * u;
@@ -156,7 +177,7 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
   for (int k = 0; k < top; ++k)
     for (int f = threadIdx.x; f < ff; f += blockDim.x) hs[k * ffp + f] = to_f(hid[((size_t)t * top + k) * ff + f]);
   __syncthreads();
-  const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
+  const float g = shared ? (sg ? 1.f / (1.f + expf(-sg[t])) : 1.f) : 0.f;  // no gate logits: the shared expert is added as it is
   const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeDownRowsPerBlock);
   for (int i = blockIdx.y * kMoeDownRowsPerBlock + warp; i < i_end; i += nw) {
     float tot = 0.f;
@@ -189,15 +210,34 @@ extern "C" int pk_router_grouped_topk(const float* logits, int* ids, float* weig
 
 extern "C" int pk_moe_up_act(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int act, int f32,
                              pk_stream st) {
-  if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || act < 0 || act > 1) return -1;
+  if (act < 0 || act > 1) return -1;
+  return pk_moe_up_act_p(xa, w_up, ids, hid, tokens, top, width, ff, act, 0.f, 0.f, f32, st);
+}
+
+extern "C" int pk_moe_up_act_p(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int act, float p0,
+                               float p1, int f32, pk_stream st) {
+  if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || act < 0 || act > 2 || (act == 2 && !(p0 > 0.f))) return -1;
   const size_t smem = (size_t)width * sizeof(float);
   const dim3 grid(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock);
-#define PK_UP(E, G) launch(moe_up_kernel<E, G>, grid, dim3(256), smem, st, true, (const E*)xa, (const E*)w_up, ids, (E*)hid, width, ff)
-  if (f32 && act) PK_UP(float, 1);
-  else if (f32) PK_UP(float, 0);
-  else if (act) PK_UP(bf16, 1);
-  else PK_UP(bf16, 0);
+#define PK_UP(E, G) launch(moe_up_kernel<E, G>, grid, dim3(256), smem, st, true, (const E*)xa, (const E*)w_up, ids, (E*)hid, width, ff, p0, p1)
+  if (f32) {
+    if (act == 2) PK_UP(float, 2);
+    else if (act) PK_UP(float, 1);
+    else PK_UP(float, 0);
+  } else {
+    if (act == 2) PK_UP(bf16, 2);
+    else if (act) PK_UP(bf16, 1);
+    else PK_UP(bf16, 0);
+  }
 #undef PK_UP
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_router_topk_logits(const float* logits, int ld, const float* bias, int* ids, float* weights, int tokens, int experts, int top,
+                                     float scale, pk_stream st) {
+  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || top > experts || ld < experts) return -1;
+  launch(router_grouped_topk_kernel, dim3(tokens), dim3(32), (size_t)(2 * experts + 2) * sizeof(float), st, true, logits, ld, bias, ids, weights, experts,
+         top, 1, 1, scale, 2, 1, 0);
   return (int)cudaGetLastError();
 }
 
@@ -208,7 +248,7 @@ extern "C" int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids,
 
 extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,
                                    const float* shared_gate, float* y, int tokens, int top, int width, int ff, int f32, pk_stream st) {
-  if (!hid || !w_down || !ids || !weights || !y || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || (shared && !shared_gate)) return -1;
+  if (!hid || !w_down || !ids || !weights || !y || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0) return -1;
   const size_t smem = (size_t)top * ((ff + 3) & ~3) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (f32) {

@@ -6,6 +6,7 @@
 //                            vary from run to run; every row's result is independent of its slot, so outputs do not.
 //   2. moe_grouped_gemm<0>   hid[slot] = relu(W_up[e] x[token(slot)])^2          (rows gathered through the slot list)
 //      moe_grouped_gemm<2>   hid[slot] = silu(W_gate[e] x) * (W_up[e] x)            (gated experts, gate / up rows interleaved)
+//      moe_grouped_gemm<3>   hid[slot] = g logistic(p1 g) (u + 1), g = min(W_gate[e] x, p0), u = clamp(W_up[e] x, -p0, p0)
 //   3. moe_grouped_gemm<1>   part[slot] = weight(pair) * W_down[e] hid[slot]     (fp32)
 //   4. moe_combine_kernel    y[t] = sum_k part[slot(t, k)] (+ logistic(g_t) * shared[t]), summed in the order of k
 // GEMM tiles: 64 rows x 64 outputs x 64 deep, 4 warps of 32 x 32, mma.sync m16n8k16 bf16 with fp32 accumulation, operands
@@ -58,12 +59,13 @@ __global__ void moe_bucket_kernel(const int* __restrict__ ids, int pairs, int ex
 
 // EPI 0: out bf16 [slots][N] = relu(acc)^2.   EPI 1: out fp32 [slots][N] = acc * weights[pair of the slot].
 // EPI 2: W rows interleaved (2f = gate f, 2f + 1 = up f): out bf16 [slots][N / 2] = silu(acc[2f]) * acc[2f + 1].
+// EPI 3: the same rows with clamped pre-activations: g = min(acc[2f], p0), u = clamp(acc[2f + 1], -p0, p0), out = g logistic(p1 g) (u + 1).
 // A row of slot s: A + (gather_div ? slot_pair[s] / gather_div : s) * K.
 template <int EPI>
 __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, void* __restrict__ out,
                                                               const int* __restrict__ meta, const int* __restrict__ slot_pair,
                                                               const float* __restrict__ weights, int experts, int max_tiles, int N, int K,
-                                                              int gather_div) {
+                                                              int gather_div, float p0, float p1) {
   __shared__ __align__(16) bf16 As[2][kGT * kGLd];
   __shared__ __align__(16) bf16 Bs[2][kGT * kGLd];
   pdl_wait();
@@ -140,6 +142,10 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
           else if (n < N) o[0] = f2bf(v0 * v0);
         } else if (EPI == 2) {
           if (n + 1 < N) static_cast<bf16*>(out)[(size_t)s * (N / 2) + n / 2] = f2bf(v0 / (1.f + expf(-v0)) * v1);
+        } else if (EPI == 3) {
+          v0 = fminf(v0, p0);
+          v1 = fminf(fmaxf(v1, -p0), p0);
+          if (n + 1 < N) static_cast<bf16*>(out)[(size_t)s * (N / 2) + n / 2] = f2bf(v0 / (1.f + expf(-p1 * v0)) * (v1 + 1.f));
         } else {
           float* o = static_cast<float*>(out) + (size_t)s * N + n;
           if (n + 1 < N) *reinterpret_cast<float2*>(o) = make_float2(v0 * wgt, v1 * wgt);
@@ -154,7 +160,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ part, const int* __
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x;
-  const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
+  const float g = shared ? (sg ? 1.f / (1.f + expf(-sg[t])) : 1.f) : 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc += part[(size_t)pair_slot[(size_t)t * top + k] * width + i];
@@ -179,7 +185,16 @@ extern "C" long pk_moe_grouped_workspace_bytes(int tokens, int top, int experts,
 extern "C" int pk_moe_grouped_act(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
                                   const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act,
                                   pk_stream st) {
-  if (!xa || !w_up || !w_down || !ids || !weights || !y || !workspace || tokens <= 0 || top <= 0 || experts <= 0 || experts > 4096 || (shared && !shared_gate) || act < 0 || act > 1)
+  if (act < 0 || act > 1) return -1;
+  return pk_moe_grouped_act_p(xa, w_up, w_down, ids, weights, shared, shared_gate, y, workspace, tokens, top, experts, width, ff, act, 0.f, 0.f, st);
+}
+
+// act 2: clamped gated experts (limit p0, slope p1); shared_gate may be NULL with a shared expert (added without a gate)
+extern "C" int pk_moe_grouped_act_p(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                                    const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act,
+                                    float p0, float p1, pk_stream st) {
+  if (!xa || !w_up || !w_down || !ids || !weights || !y || !workspace || tokens <= 0 || top <= 0 || experts <= 0 || experts > 4096 || act < 0 || act > 2 ||
+      (act == 2 && !(p0 > 0.f)))
     return -1;
   if (width % 8 || ff % 8 || (reinterpret_cast<uintptr_t>(xa) & 15) || (reinterpret_cast<uintptr_t>(w_up) & 15) ||
       (reinterpret_cast<uintptr_t>(w_down) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
@@ -196,14 +211,17 @@ extern "C" int pk_moe_grouped_act(const void* xa, const void* w_up, const void* 
   float* part = reinterpret_cast<float*>(ws + o);
   launch(moe_bucket_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), st, true, ids, (int)pairs, experts, max_tiles, meta, slot_pair,
          pair_slot);
-  if (act == 1)
+  if (act == 2)
+    launch(moe_grouped_gemm_kernel<3>, dim3((2 * ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
+           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, 2 * ff, width, top, p0, p1);
+  else if (act == 1)
     launch(moe_grouped_gemm_kernel<2>, dim3((2 * ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
-           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, 2 * ff, width, top);
+           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, 2 * ff, width, top, 0.f, 0.f);
   else
     launch(moe_grouped_gemm_kernel<0>, dim3((ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
-           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, ff, width, top);
+           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, ff, width, top, 0.f, 0.f);
   launch(moe_grouped_gemm_kernel<1>, dim3((width + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)hid, (const bf16*)w_down,
-         (void*)part, (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, width, ff, 0);
+         (void*)part, (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, width, ff, 0, 0.f, 0.f);
   launch(moe_combine_kernel, dim3(tokens), dim3(256), 0, st, true, (const float*)part, (const int*)pair_slot, (const bf16*)shared, shared_gate, y, width,
          top);
   return (int)cudaGetLastError();

@@ -4,7 +4,9 @@
 //   * xLSTM matrix memory: m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k alone;
 //                          o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)        (i, f soft-capped log gates, m starts at 0)
 //     slot layout: S [H][dim][vdim], n [H][dim], m [H][vdim + 1] (every column keeps its own copy of the running maximum)
-//   * per-head RMS norm of the read-out times a weight times an activation of a gate projection.
+//   * state-space duality (scalar decay per head):  S <- e^(-e^(A_log) dt) S + dt B x^T;  y = S^T C + D x,  dt = softplus(. + dt_bias)
+//     (B, C of the head's group [state], x the head's slice [vdim]; the state S [state][vdim] takes the place of [dim][vdim])
+//   * per-head RMS norm of the read-out times a weight times an activation of a gate projection (or the gate first, then the norm).
 // State, gates, decays, unit norms and the recurrences are fp32 whatever the element type E of the activations is.
 //
 // Step layout: entry e of the step owns rows [row0[e], row0[e] + len[e]) of every [tokens, features] buffer (a portion
@@ -23,10 +25,10 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float logsigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-// y[t][c] = silu(sum_j w[c][j] * x[t - (taps-1-j)][c]); inputs before this step's rows come from the slot's state
+// y[t][c] = silu(bias[c] + sum_j w[c][j] * x[t - (taps-1-j)][c]) (bias may be null); inputs before this step's rows come from the slot's state
 // [taps-1][C] (oldest first; zero for a new request).  in / out may have different row strides; out may alias nothing of in.
 template <typename E>
-__global__ void causal_conv_silu_kernel(const E* __restrict__ in, int ld_in, const E* __restrict__ w, const float* __restrict__ state, long slot_stride,
+__global__ void causal_conv_silu_kernel(const E* __restrict__ in, int ld_in, const E* __restrict__ w, const E* __restrict__ bias, const float* __restrict__ state, long slot_stride,
                                         const int* __restrict__ req, const int* __restrict__ slot, const int* __restrict__ row0, E* __restrict__ out,
                                         int ld_out, int C, int taps, long total) {
   pdl_wait();
@@ -34,7 +36,7 @@ __global__ void causal_conv_silu_kernel(const E* __restrict__ in, int ld_in, con
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const int t = (int)(i / C), c = (int)(i % C), e = req[t], off = t - row0[e];
     const float* st = state + (size_t)slot[e] * slot_stride;
-    float acc = 0.f;
+    float acc = bias ? to_f(bias[c]) : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int back = taps - 1 - j;
       const float x = off - back >= 0 ? to_f(in[(size_t)(t - back) * ld_in + c]) : st[(size_t)(taps - 1 + off - back) * C + c];
@@ -73,9 +75,12 @@ struct SeqArgs {
   float* den;          // matrix memory: [tokens, H] divisor
   int H, G, dim, vdim;
   float cap;           // matrix memory: gate soft cap
+  const void* dt;      // state space: [tokens, ld_dt] element type, step-size projection of head h at dt_off + h
+  int ld_dt, dt_off;
+  const float* p2;     // state space: skip weight D [H]  (p0 = A_log, p1 = dt_bias)
 };
 
-// MODE 0: gated delta rule.  MODE 1: xLSTM matrix memory.
+// MODE 0: gated delta rule.  MODE 1: xLSTM matrix memory.  MODE 2: state-space duality (q = C, k = B, v = x; dim = state size).
 // Thread layout: KS = DK / 16 neighbouring lanes share one state column, each holding 16 of its DK entries in registers
 // (entry (m * KS + ks) * 4 + e for m < 4, e < 4, so that the lanes' 16-byte reads of k / q from shared memory fall on
 // consecutive banks); the two dot products per token are finished with log2(KS) shuffles.  128 / KS columns per CTA; the
@@ -158,7 +163,13 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
       const int tt = i / COLS, c = i % COLS;
       vs[tt][c] = col0 + c < vdim ? to_f(Xb[(size_t)tt * a.ld + a.v_off + h * vdim + col0 + c]) : 0.f;
     }
-    if (tid < nb) {
+    if (MODE == 2) {
+      if (tid < nb) {  // step size and decay of the head at this token, from the projection's output
+        const float step = softplusf_(to_f(static_cast<const E*>(a.dt)[(size_t)(r0 + b0 + tid) * a.ld_dt + a.dt_off + h]) + a.p1[h]);
+        g0[tid] = expf(-expf(a.p0[h]) * step);
+        g1[tid] = step;
+      }
+    } else if (tid < nb) {
       const size_t row = (size_t)(r0 + b0 + tid);
       const float za = a.z[row * a.ldz + a.za_off + h], zb = a.z[row * a.ldz + a.zb_off + h];
       if (MODE == 0) {  // za: decay projection, zb: write-strength projection
@@ -171,7 +182,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
     }
     __syncthreads();
     // 2. unit vectors (delta rule) and the query's scale
-    for (int tt = warp; tt < nb; tt += nw) {
+    for (int tt = warp; MODE != 2 && tt < nb; tt += nw) {
       float qf = qscale, kf = 1.f;
       if (MODE == 0) {
         float qq = 0.f, kk = 0.f;
@@ -235,6 +246,25 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
 #pragma unroll
         for (int s = 1; s < KS; s <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
         if (is_v && ksi == 0) a.out[row * out_ld + h * vdim + col] = o;
+      } else if (MODE == 2) {
+        const float fa = g0[tt], wb = g1[tt] * vt;
+#pragma unroll
+        for (int mi = 0; mi < NS / 4; ++mi) {
+          const float4 k4 = k4p[mi * KS];
+          const float4 q4 = q4p[mi * KS];
+          S[mi * 4] = fmaf(k4.x, wb, fa * S[mi * 4]);
+          S[mi * 4 + 1] = fmaf(k4.y, wb, fa * S[mi * 4 + 1]);
+          S[mi * 4 + 2] = fmaf(k4.z, wb, fa * S[mi * 4 + 2]);
+          S[mi * 4 + 3] = fmaf(k4.w, wb, fa * S[mi * 4 + 3]);
+          o0 = fmaf(S[mi * 4], q4.x, o0);
+          o1 = fmaf(S[mi * 4 + 1], q4.y, o1);
+          o2 = fmaf(S[mi * 4 + 2], q4.z, o2);
+          o3 = fmaf(S[mi * 4 + 3], q4.w, o3);
+        }
+        float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+        for (int s = 1; s < KS; s <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
+        if (is_v && ksi == 0) a.out[row * out_ld + h * vdim + col] = fmaf(a.p2[h], vt, o);
       } else {
         const float f = g0[tt], ig = g1[tt];
         const float mn = fmaxf(f + m, ig);
@@ -275,7 +305,8 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
 }
 
 // out[t, h, j] = E( (o[t,h,j] / den[t,h]) / sqrt(mean_j(.^2) + eps) * w[h * w_stride + j] * act(gate[t, gate_off + h*vdim + j]) )
-// act 0: silu, 1: logistic.  den may be null.  One warp per (token, head).
+// act 0: silu, 1: logistic.  act 2: the silu gate comes BEFORE the norm, out = rms_norm(o * silu(gate)) * w.  den may be null.
+// One warp per (token, head); "head" may be any equal part of the row (norm groups).
 template <typename E>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ den, const E* __restrict__ w, int w_stride,
                                       const E* __restrict__ gate, int ld_gate, int gate_off, E* __restrict__ out, int H, int vdim, float eps, int act,
@@ -290,7 +321,11 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   const float* orow = o + pr * vdim;
   float ss = 0.f;
   for (int j = lane; j < vdim; j += 32) {
-    const float v = den ? orow[j] / den[pr] : orow[j];
+    float v = den ? orow[j] / den[pr] : orow[j];
+    if (act == 2) {
+      const float gz = to_f(gate[(size_t)t * ld_gate + gate_off + h * vdim + j]);
+      v *= gz / (1.f + expf(-gz));
+    }
     ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
@@ -298,8 +333,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   for (int j = lane; j < vdim; j += 32) {
     const float v = den ? orow[j] / den[pr] : orow[j];
     const float gz = to_f(gate[(size_t)t * ld_gate + gate_off + h * vdim + j]);
-    const float ga = act == 0 ? gz / (1.f + expf(-gz)) : 1.f / (1.f + expf(-gz));
-    out[pr * vdim + j] = from_f<E>(v * inv * to_f(w[(size_t)h * w_stride + j]) * ga);
+    const float ga = act == 1 ? 1.f / (1.f + expf(-gz)) : gz / (1.f + expf(-gz));
+    out[pr * vdim + j] = from_f<E>(act == 2 ? (v * ga) * inv * to_f(w[(size_t)h * w_stride + j]) : v * inv * to_f(w[(size_t)h * w_stride + j]) * ga);
   }
 }
 
@@ -325,14 +360,20 @@ using namespace pk;
 extern "C" int pk_causal_conv_silu(const void* in, int ld_in, const void* w, float* state, long slot_stride, const int* req, const int* slot,
                                    const int* row0, const int* len, void* out, int ld_out, int channels, int taps, int tokens, int entries, int f32,
                                    pk_stream st) {
+  return pk_causal_conv_silu_bias(in, ld_in, w, nullptr, state, slot_stride, req, slot, row0, len, out, ld_out, channels, taps, tokens, entries, f32, st);
+}
+
+extern "C" int pk_causal_conv_silu_bias(const void* in, int ld_in, const void* w, const void* bias, float* state, long slot_stride, const int* req,
+                                        const int* slot, const int* row0, const int* len, void* out, int ld_out, int channels, int taps, int tokens,
+                                        int entries, int f32, pk_stream st) {
   if (!in || !w || !state || !req || !slot || !row0 || !len || !out || channels <= 0 || taps <= 0 || tokens <= 0 || entries <= 0) return -1;
   const long total = (long)tokens * channels;
   if (f32)
-    launch(causal_conv_silu_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, st, true, (const float*)in, ld_in, (const float*)w, (const float*)state,
-           slot_stride, req, slot, row0, (float*)out, ld_out, channels, taps, total);
+    launch(causal_conv_silu_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, st, true, (const float*)in, ld_in, (const float*)w, (const float*)bias,
+           (const float*)state, slot_stride, req, slot, row0, (float*)out, ld_out, channels, taps, total);
   else
-    launch(causal_conv_silu_kernel<bf16>, dim3(grid_for(total, 256)), dim3(256), 0, st, true, (const bf16*)in, ld_in, (const bf16*)w, (const float*)state,
-           slot_stride, req, slot, row0, (bf16*)out, ld_out, channels, taps, total);
+    launch(causal_conv_silu_kernel<bf16>, dim3(grid_for(total, 256)), dim3(256), 0, st, true, (const bf16*)in, ld_in, (const bf16*)w, (const bf16*)bias,
+           (const float*)state, slot_stride, req, slot, row0, (bf16*)out, ld_out, channels, taps, total);
   if (taps > 1) {
     const dim3 g((channels + 255) / 256, entries);
     if (f32) launch(conv_state_update_kernel<float>, g, dim3(256), 0, st, true, (const float*)in, ld_in, state, slot_stride, slot, row0, len, channels, taps);
@@ -367,7 +408,7 @@ extern "C" int pk_mlstm_seq(const void* qkv, int ld, int q_off, int k_off, int v
 
 extern "C" int pk_head_norm_gate(const float* o, const float* den, const void* w, int w_stride, const void* gate, int ld_gate, int gate_off, void* out,
                                  int tokens, int heads, int vdim, float eps, int act, int f32, pk_stream st) {
-  if (!o || !w || !gate || !out || tokens <= 0 || heads <= 0 || vdim <= 0 || act < 0 || act > 1) return -1;
+  if (!o || !w || !gate || !out || tokens <= 0 || heads <= 0 || vdim <= 0 || act < 0 || act > 2) return -1;
   const long pairs = (long)tokens * heads;
   const dim3 g((unsigned)((pairs + 3) / 4));
   if (f32)
@@ -377,4 +418,15 @@ extern "C" int pk_head_norm_gate(const float* o, const float* den, const void* w
     launch(head_norm_gate_kernel<bf16>, g, dim3(128), 0, st, true, o, den, (const bf16*)w, w_stride, (const bf16*)gate, ld_gate, gate_off, (bf16*)out, heads,
            vdim, eps, act, pairs);
   return (int)cudaGetLastError();
+}
+
+extern "C" int pk_ssd_seq(const void* xbc, int ld, int x_off, int b_off, int c_off, const void* dt, int ld_dt, int dt_off, const float* a_log,
+                          const float* dt_bias, const float* d_skip, float* state, long slot_stride, const int* slot, const int* row0, const int* len,
+                          float* out, int heads, int groups, int state_dim, int vdim, int entries, int f32, pk_stream st) {
+  if (!xbc || !dt || !a_log || !dt_bias || !d_skip || !state || !slot || !row0 || !len || !out || heads <= 0 || groups <= 0 || heads % groups ||
+      state_dim <= 0 || vdim <= 0 || entries <= 0)
+    return -1;
+  SeqArgs a{xbc, ld, c_off, b_off, x_off, nullptr, 0, 0, 0, a_log, dt_bias, state, slot_stride, slot, row0, len, out, nullptr,
+            heads, groups, state_dim, vdim, 0.f, dt, ld_dt, dt_off, d_skip};
+  return f32 ? launch_seq<float, 2>(a, entries, st) : launch_seq<bf16, 2>(a, entries, st);
 }

@@ -434,6 +434,104 @@ __global__ void gnorm_rows_kernel(const float* __restrict__ x, const int* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)blockIdx.x * width + i] = from_f<E>(row[i] * inv_s[i / gsz] * to_f(w[i]));
 }
 
+// ---- pre-norm blocks with plain-weight RMS norms: h = x / sqrt(mean(x^2) + eps) * w feeds a sublayer, whose result is added to x.
+// A sublayer's result may be the sum of up to two branches, each optionally RMS-normed over the row with its own weight first:
+//   x <- x + mult * (branch(ya, wa) + branch(yb, wb)),  branch(y, w) = w ? y / sqrt(mean(y^2) + eps) * w : y;   h = rms(x) * w_next
+// One CTA per token; rows live in shared memory as fp32; sums of squares are added in a fixed order (group_inv_rms with one group).
+
+// x[t] = embed[ids[t]] * scale;  h[t] = rms(x[t]) * w_next in the element type (and unrounded in h32 when that is not null)
+template <typename E>
+__global__ void embed_scaled_norm_kernel(const E* __restrict__ embed, const int* __restrict__ tok, float scale, float* __restrict__ x,
+                                         const E* __restrict__ w_next, E* __restrict__ h, float* __restrict__ h32, int width, float eps) {
+  extern __shared__ float gn_sm[];
+  float* row = gn_sm;
+  float* inv_s = row + width;
+  float* part_s = inv_s + 1;
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x;
+  const E* src = embed + (size_t)tok[t] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_f(src[i]) * scale;
+    row[i] = v;
+    x[(size_t)t * width + i] = v;
+  }
+  if (!w_next) return;
+  group_inv_rms(row, width, 1, eps, part_s, inv_s);
+  const float inv = inv_s[0];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = row[i] * inv * to_f(w_next[i]);
+    h[(size_t)t * width + i] = from_f<E>(v);
+    if (h32) h32[(size_t)t * width + i] = v;
+  }
+}
+
+template <typename E, typename Y>
+__global__ void branches_add_norm_kernel(const Y* __restrict__ ya, const E* __restrict__ wa, const E* __restrict__ yb, const E* __restrict__ wb, float mult,
+                                         float* __restrict__ x, const E* __restrict__ w_next, E* __restrict__ h, float* __restrict__ h32, int width,
+                                         float eps) {
+  extern __shared__ float gn_sm[];
+  float* row = gn_sm;         // branch a, then the new residual row
+  float* rowb = row + width;  // branch b
+  float* inv_s = rowb + width;
+  float* part_s = inv_s + 1;
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x;
+  const size_t at = (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    row[i] = ya ? to_f(ya[at + i]) : 0.f;
+    rowb[i] = yb ? to_f(yb[at + i]) : 0.f;
+  }
+  float inv_a = 1.f, inv_b = 1.f;
+  if (ya && wa) {
+    group_inv_rms(row, width, 1, eps, part_s, inv_s);
+    inv_a = inv_s[0];
+  }
+  if (yb && wb) {
+    group_inv_rms(rowb, width, 1, eps, part_s, inv_s);
+    inv_b = inv_s[0];
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float a = ya ? (wa ? row[i] * inv_a * to_f(wa[i]) : row[i]) : 0.f;
+    const float b = yb ? (wb ? rowb[i] * inv_b * to_f(wb[i]) : rowb[i]) : 0.f;
+    const float r = x[at + i] + mult * (a + b);
+    x[at + i] = r;
+    row[i] = r;
+  }
+  if (!w_next) return;
+  group_inv_rms(row, width, 1, eps, part_s, inv_s);
+  const float inv = inv_s[0];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = row[i] * inv * to_f(w_next[i]);
+    h[at + i] = from_f<E>(v);
+    if (h32) h32[at + i] = v;
+  }
+}
+
+// out = cap * tanh(float(in) * scale / cap)  (cap 0: float(in) * scale)
+template <typename A>
+__global__ void logits_scale_cap_kernel(const A* __restrict__ in, float* __restrict__ out, long n, float scale, float cap) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float z = to_f(in[i]) * scale;
+    out[i] = cap > 0.f ? cap * tanhf(z / cap) : z;
+  }
+}
+
+// in [T, 2F] = [gate | up]: g = min(gate, limit), u = clamp(up, -limit, limit), out = g * logistic(slope * g) * (u + 1)
+template <typename E>
+__global__ void act_clamped_kernel(const E* __restrict__ in, E* __restrict__ out, int F, long total, float limit, float slope) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / F, f = i % F;
+    const float g = fminf(to_f(in[t * 2 * F + f]), limit), u = fminf(fmaxf(to_f(in[t * 2 * F + F + f]), -limit), limit);
+    out[i] = from_f<E>(g / (1.f + expf(-slope * g)) * (u + 1.f));
+  }
+}
+
 // threads per row: about two entries per thread for a few rows (every dependent round of loads costs a memory latency, and a step of
 // one token is nothing but such rounds), 256 for many rows
 static inline int gnorm_threads(int width, int tokens) {
@@ -626,5 +724,53 @@ extern "C" int pk_res32_gnorm_rows(const float* x, const int* rows, const void* 
   if (!(f32 ? gnorm_fits(gnorm_rows_kernel<float>, sm) : gnorm_fits(gnorm_rows_kernel<bf16>, sm))) return -2;
   PK_BY_TYPE(f32, launch(gnorm_rows_kernel<float>, dim3(n_rows), dim3(gnorm_threads(width, n_rows)), sm, st, true, x, rows, (const float*)w, (float*)out, width, groups, eps),
              launch(gnorm_rows_kernel<bf16>, dim3(n_rows), dim3(gnorm_threads(width, n_rows)), sm, st, true, x, rows, (const bf16*)w, (bf16*)out, width, groups, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_embed_scaled_norm(const void* embed, const int* token_ids, float scale, float* x, const void* w_next, void* h, float* h32,
+                                          int width, float eps, int tokens, int f32, pk_stream st) {
+  if (!embed || !token_ids || !x || (w_next && !h) || width <= 0 || tokens <= 0) return -1;
+  const size_t sm = gnorm_smem(width, 1);
+  if (!(f32 ? gnorm_fits(embed_scaled_norm_kernel<float>, sm) : gnorm_fits(embed_scaled_norm_kernel<bf16>, sm))) return -2;
+  const dim3 g(tokens), b(gnorm_threads(width, tokens));
+  PK_BY_TYPE(f32, launch(embed_scaled_norm_kernel<float>, g, b, sm, st, true, (const float*)embed, token_ids, scale, x, (const float*)w_next, (float*)h, h32, width, eps),
+             launch(embed_scaled_norm_kernel<bf16>, g, b, sm, st, true, (const bf16*)embed, token_ids, scale, x, (const bf16*)w_next, (bf16*)h, h32, width, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_branches_add_norm(const void* ya, int ya_is_f32, const void* wa, const void* yb, const void* wb, float mult, float* x,
+                                          const void* w_next, void* h, float* h32, int width, float eps, int tokens, int f32, pk_stream st) {
+  if (!x || (w_next && !h) || width <= 0 || tokens <= 0) return -1;
+  const size_t sm = gnorm_smem(2 * width, 1);
+  const dim3 g(tokens), b(gnorm_threads(width, tokens));
+  if (f32) {
+    if (!gnorm_fits(branches_add_norm_kernel<float, float>, sm)) return -2;
+    launch(branches_add_norm_kernel<float, float>, g, b, sm, st, true, (const float*)ya, (const float*)wa, (const float*)yb, (const float*)wb, mult, x,
+           (const float*)w_next, (float*)h, h32, width, eps);
+  } else if (ya_is_f32) {
+    if (!gnorm_fits(branches_add_norm_kernel<bf16, float>, sm)) return -2;
+    launch(branches_add_norm_kernel<bf16, float>, g, b, sm, st, true, (const float*)ya, (const bf16*)wa, (const bf16*)yb, (const bf16*)wb, mult, x,
+           (const bf16*)w_next, (bf16*)h, h32, width, eps);
+  } else {
+    if (!gnorm_fits(branches_add_norm_kernel<bf16, bf16>, sm)) return -2;
+    launch(branches_add_norm_kernel<bf16, bf16>, g, b, sm, st, true, (const bf16*)ya, (const bf16*)wa, (const bf16*)yb, (const bf16*)wb, mult, x,
+           (const bf16*)w_next, (bf16*)h, h32, width, eps);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_logits_scale_cap(const void* in, int in_f32, float* out, long n, float scale, float cap, pk_stream st) {
+  if (!in || !out || n <= 0 || cap < 0.f) return -1;
+  const dim3 g(grid_1d(n, 256)), b(256);
+  if (in_f32) launch(logits_scale_cap_kernel<float>, g, b, 0, st, true, (const float*)in, out, n, scale, cap);
+  else launch(logits_scale_cap_kernel<bf16>, g, b, 0, st, true, (const bf16*)in, out, n, scale, cap);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_act_clamped(const void* in, void* out, int F, int tokens, float limit, float slope, int f32, pk_stream st) {
+  if (!in || !out || F <= 0 || tokens <= 0 || !(limit > 0.f)) return -1;
+  const long total = (long)F * tokens;
+  PK_BY_TYPE(f32, launch(act_clamped_kernel<float>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const float*)in, (float*)out, F, total, limit, slope),
+             launch(act_clamped_kernel<bf16>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const bf16*)in, (bf16*)out, F, total, limit, slope));
   return (int)cudaGetLastError();
 }
