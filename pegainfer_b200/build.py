@@ -50,6 +50,7 @@ PARTS_OF = {
     "Nagosun": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "gqa_attention.cu", "latent_attention.cu", "latent_attention_mma.cu"),
                 ("qwen3_host.cpp", "layered_host.cpp")),
 }
+PARTS_OF["Goguzen"] = PARTS_OF["Risolorn"]  # the same files: attention, recurrent mixers, experts on the fp32 residual stream
 MANIFEST = os.path.join(OBJ, "linked.txt")
 
 

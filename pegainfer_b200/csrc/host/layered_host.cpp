@@ -1,15 +1,22 @@
-// C++ host of the decoder designs whose checkpoint configuration lists the layers one by one (Vamadra, Risolorn, Nagosun), on an
-// fp32 residual stream.  A layer is a mixer plus an optional feed-forward, put together in one of three block forms:
+// C++ host of the decoder designs whose checkpoint configuration lists the layers one by one (Vamadra, Risolorn, Nagosun, Goguzen), on an
+// fp32 residual stream.  A layer is a mixer plus an optional feed-forward, put together in one of four block forms:
 //   block 0  sequential sublayers with the norm on each sublayer's OUTPUT:  x += norm(mixer(x));  x += norm(ff(x))
 //   block 1  parallel sublayers under one Dynamic-Tanh pre-norm:            h = dyt(x);  x += mixer(h) + ff(h)
 //   block 2  "sandwich": a grouped RMS norm before AND after each sublayer, the sublayer's result gated by a logistic
 //            projection of its input, the sum scaled:  h = gn(x); x += m * gn(f(h) * logistic(W_rg h + b))   (mixers 0 and 1)
+//   block 3  pre-norm sequential sublayers with plain-weight RMS norms:      x += mixer(rms(x) w1);  x += ff(rms(x) w2)   (mixers 1 and 4);
+//            a layer may run with another layer's weights (and a cache / state of its own); logits are scaled and soft-capped
 // Mixers: 0 latent attention (compressed paged cache, shared rotated key part, per-head sink, logistic output gate, optional
 // reuse of an earlier layer's cache); 1 grouped-query attention with biases, rotary embedding from a frequency table, a
 // chunk-local causal mask and a sink, over a paged K/V cache (block 2 adds: sliding window, score soft cap, linear distance
 // bias, unit-RMS cached values, a sink of score zero, an element-wise output gate); 2 gated delta rule behind short causal
-// convolutions; 3 xLSTM matrix memory.  Mixers 2 and 3 keep an fp32 state per request in numbered state slots.  Feed-forward: dense SwiGLU or a
-// mixture of experts (softmax or logistic router, relu^2 or gated-SiLU experts).
+// convolutions; 3 xLSTM matrix memory; 4 two branches side by side on the same input -- grouped-query attention and a state-space layer
+// (scalar decay per head, short causal convolution, gated group-normed read-out) -- each branch's result RMS-normed over the width, the
+// mixer's result their mean.  Block 3 gives the attention (mixer 1 and the attention branch of 4) further options: RMS norm of q and k per
+// head or over the whole projection, a query factor that grows with the logarithm of the position, values that are the keys as projected,
+// a window that keeps the first positions visible, rotary frequencies rescaled by wavelength.  Mixers 2, 3 and 4 keep an fp32 state per
+// request in numbered state slots.  Feed-forward: dense SwiGLU or a mixture of experts (softmax or logistic router or plain top logits;
+// relu^2, gated-SiLU or clamped gated experts; a shared expert with or without a gate).
 //
 // Same structure as the other hosts in this folder: kernels are reached only through the C ABI
 // (include/pegainfer_kernels.h) resolved with dlopen; paging reuses pq::PagePool / pq::KvState; a step is planned and
@@ -66,6 +73,17 @@ struct LayerCfg {  // mirrored by ctypes in pegainfer_b200/vamadra.py
   int sink_kind;             // 0 learned per-head sink 'mix.sink', 1 none, 2 a sink of score zero (one added to the softmax denominator)
   int out_gate;              // 1: 1 = heads' outputs times logistic(W_g h) element by element ('mix.g' [heads * vdim, width])
   int proj_bias;             // 1: q, k, v and o projections carry biases ('.b')
+  // options read by block 3 (all off when zero)
+  int keep_first;            // attention with a window: the first keep_first positions stay visible
+  int qk_norm;               // 1: RMS norm of q and k per head, weights 'q.norm' / 'k.norm' [dim]; 2: over the whole projection, weights [heads*dim] / [kv_heads*dim]
+  float q_temp_coef;         // q *= 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)
+  int q_temp_every;
+  int values_are_keys;       // 1: no value projection, a head's values are its keys as projected
+  int scaling_kind;          // rotary scaling (has_scaling): 0 YaRN ramp over the pair index; 1 by wavelength: s_fast = 'high', s_slow = 'low'
+  int ssm_heads, ssm_vdim, ssm_state, ssm_groups, ssm_norm_groups;  // mixer 4, state-space branch (taps in `conv`)
+  float act_limit, act_slope;  // expert_act 2: g = min(gate, limit), u = clamp(up, +-limit), g logistic(slope g) (u + 1)
+  float shared_limit;        // the shared expert's limit (router_kind 2: shared expert of the same form, no gate)
+  int weights_of;            // >= 0: the layer runs with that layer's weights
 };
 struct ModelCfg {
   int vocab, width, n_layers;
@@ -76,6 +94,7 @@ struct ModelCfg {
   int norm_groups;        // block 2: parts of a row that are normed separately
   float residual_mult;    // block 2: multiplier of every sublayer's normed result
   int gated_residual;     // block 2: sublayer results times logistic(W_rg h + b) ('rg1' / 'rg2') before their norm
+  float logit_softcap;    // block 3: logits <- cap * tanh(logits / cap) after the multiplier (0: none)
 };
 
 struct Lib {
@@ -84,19 +103,24 @@ struct Lib {
 #define PV_COMMON(X)                                                                                                                       \
   X(cuda_set_device) X(cublas_init) X(cublas_destroy) X(gemm_cuda) X(flashinfer_top1_cuda) X(pk_b200_set_pdl) X(pk_b200_launch_count)      \
   X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_proj_rows_f32out) X(pk_scale_to_f32) X(pk_top1_rows_f32)
-#define PV_MOE(X) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_moe_up_act) X(pk_moe_grouped_act)
+#define PV_MOE(X) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_moe_up_act_p) X(pk_moe_grouped_act_p)
 #define PV_DENSE(X) X(pk_act) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
 #define PV_BLOCK0(X)                                                                                                                        \
   X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_rope_slice) X(pk_latent_kv_append) X(pk_latent_attention) \
   X(pk_router_grouped_topk)
 #define PV_BLOCK1(X)                                                                                                                        \
   X(pk_res32_embed_scaled) X(pk_res32_add_dyt) X(pk_res32_dyt_rows) X(pk_gqa_rope_append) X(pk_gqa_attention) X(pk_causal_conv_silu)       \
-  X(pk_gated_delta_seq) X(pk_mlstm_seq) X(pk_head_norm_gate) X(pk_router_topk_ex)
+  X(pk_gated_delta_seq) X(pk_mlstm_seq) X(pk_router_topk_ex)
+#define PV_BLOCK13(X) X(pk_head_norm_gate)
+#define PV_BLOCK23(X) X(pk_res32_gnorm_rows) X(pk_gqa_attention_ex)
+#define PV_BLOCK3(X)                                                                                                                        \
+  X(pk_res32_embed_scaled_norm) X(pk_res32_branches_add_norm) X(pk_logits_scale_cap) X(pk_act_clamped) X(pk_gqa_norm_append)               \
+  X(pk_causal_conv_silu_bias) X(pk_ssd_seq) X(pk_router_topk_logits)
 #define PV_BLOCK2(X)                                                                                                                        \
-  X(pk_res32_embed_gnorm) X(pk_res32_gated_gnorm_add) X(pk_res32_gnorm_rows) X(pk_gqa_rope_append_ex) X(pk_gqa_attention_ex) X(pk_rope_slice_ex)   \
+  X(pk_res32_embed_gnorm) X(pk_res32_gated_gnorm_add) X(pk_gqa_rope_append_ex) X(pk_rope_slice_ex)   \
   X(pk_latent_kv_append_ex) X(pk_latent_attention_ex) X(pk_b200_gemm_segments)
 #define PV_FN(name) decltype(&::name) name = nullptr;
-  PV_COMMON(PV_FN) PV_MOE(PV_FN) PV_DENSE(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN) PV_BLOCK2(PV_FN)
+  PV_COMMON(PV_FN) PV_MOE(PV_FN) PV_DENSE(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN) PV_BLOCK2(PV_FN) PV_BLOCK13(PV_FN) PV_BLOCK23(PV_FN) PV_BLOCK3(PV_FN)
 #undef PV_FN
   // a library built for one design need not hold the other block form's kernels: only what `block_kind` runs is required
   std::string load(const std::string& p, int block_kind) {
@@ -110,9 +134,11 @@ struct Lib {
     if (block_kind == 0) {
       PV_MOE(PV_REQ) PV_DENSE(PV_REQ) PV_BLOCK0(PV_REQ)
     } else if (block_kind == 1) {
-      PV_MOE(PV_REQ) PV_BLOCK1(PV_REQ)
-    } else {  // the sandwich block form has no mixture of experts
-      PV_DENSE(PV_REQ) PV_BLOCK2(PV_REQ)
+      PV_MOE(PV_REQ) PV_BLOCK1(PV_REQ) PV_BLOCK13(PV_REQ)
+    } else if (block_kind == 2) {  // the sandwich block form has no mixture of experts
+      PV_DENSE(PV_REQ) PV_BLOCK2(PV_REQ) PV_BLOCK23(PV_REQ)
+    } else {
+      PV_MOE(PV_REQ) PV_BLOCK3(PV_REQ) PV_BLOCK13(PV_REQ) PV_BLOCK23(PV_REQ)
     }
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
@@ -137,8 +163,10 @@ struct Layer {
   // mixers 1-3 / block 1: stacked projections [q | k | v (| gate)], their bias, the few-row fp32 projections [router | za | zb]
   Mat nb, qkv, qkv_bias, small, conv_w, hnorm;
   Mat norm1b, norm2b, o_bias, rg1_bias, rg2, rg2_bias;    // block 2: post-norms, output bias, gates of the sublayer results (rg1 is stacked into qkv)
-  DeviceBuf alpha32, corr32, p0_32, p1_32;                 // float copies of small parameter vectors (made in finalize)
-  Mat alpha, corr, p0, p1;
+  DeviceBuf alpha32, corr32, p0_32, p1_32, p2_32;          // float copies of small parameter vectors (made in finalize)
+  Mat alpha, corr, p0, p1, p2;
+  Mat qn, kn, conv_b, o2, lout, rout;                      // block 3: q / k norm weights; mixer 4: convolution bias, second output projection, branch norms
+  int wsrc = 0;                                            // the layer whose weights this layer runs with (itself unless the configuration says otherwise)
   int64_t state_off = 0;                                   // float offset of the layer's block inside a state slot
   DeviceBuf freq;                                          // [rot_dims / 2] fp32 angular frequencies
   float mag = 1.f;
@@ -169,6 +197,7 @@ struct Model {
   // per-step scratch, grown to the largest step seen
   int cap_t = 0, cap_r = 0;
   DeviceBuf h32, big, convo, zs, orec, den;  // block 1: unrounded norm output, stacked projections, conv outputs, few-row fp32, read-out
+  DeviceBuf ao2, mix2;                       // mixer 4: the state-space branch's gated read-out and its projection
   DeviceBuf x, xa, q, dkv, qa, gate, olat, ao, mix, gu, act, z, ids, wts, hid, yf, sgl, sh, xr, logits_e, logits_f, logits_bf, sampled_d, top1_val,
       top1_states, trail, moe_ws;
   DeviceBuf meta_d;
@@ -184,7 +213,7 @@ struct Model {
   std::set<GraphKey> seen;
   bool use_graph = true;
   // widest layer
-  int mx_big = 0, mx_conv = 0, mx_small = 0;
+  int mx_big = 0, mx_conv = 0, mx_small = 0, mx_inner = 0;
   int mx_q = 0, mx_dkv = 0, mx_qa = 0, mx_h = 0, mx_olat = 0, mx_ao = 0, mx_gu = 0, mx_act = 0, mx_e = 0, mx_top = 0, mx_hid = 0;
 
   bool fail(const std::string& m) {
@@ -219,7 +248,8 @@ struct Model {
   bool put_rows(Mat& m, int rows, int cols, int row0, int row_step, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols);
   bool to_f32(const Mat& m, DeviceBuf* out);
   bool put_uk(Layer& L, const void* data, const std::string& name, int rows, int cols);
-  bool run_experts(Layer& L, int T, const void* shared);
+  bool run_experts(const Layer& L, int T, const void* shared, const float* shared_gate);
+  bool run_prenorm_layer(int li, int T, int max_kv, const int* M, int n);
   bool run_parallel_layer(int li, int T, const int* M, int n);
   bool run_sandwich_layer(int li, int T, int max_kv, const int* M);
   bool lin_segments(const Mat& W, const void* X, void* const* Y, const int* seg_rows, int N);
@@ -240,7 +270,8 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
   c = mc;
   es = c.f32 ? 4 : 2;
   if (c.vocab <= 0 || c.width <= 0 || c.n_layers <= 0) return fail("vocab, width and the number of layers must be positive");
-  if (c.block_kind < 0 || c.block_kind > 2) return fail("unknown block form");
+  if (c.block_kind < 0 || c.block_kind > 3) return fail("unknown block form");
+  if (c.block_kind == 3 && c.logit_softcap < 0.f) return fail("logit_softcap must not be negative");
   if (c.block_kind == 2 && (c.norm_groups <= 0 || c.width % c.norm_groups)) return fail("norm.groups must divide the width");
   if (c.page_size <= 0) c.page_size = 16;
   if (c.max_requests <= 0) c.max_requests = 4;
@@ -250,8 +281,20 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     Layer& L = layers[i];
     L.c = lc[i];
     const LayerCfg& a = L.c;
-    if (a.mixer_kind < 0 || a.mixer_kind > 3) return fail(lname(i, "mixer: unknown kind"));
-    if (c.block_kind == 2 ? a.mixer_kind > 1 : (a.mixer_kind == 0) != (c.block_kind == 0)) return fail(lname(i, "mixer: not available in this block form"));
+    if (a.mixer_kind < 0 || a.mixer_kind > 4) return fail(lname(i, "mixer: unknown kind"));
+    if (c.block_kind == 3 ? (a.mixer_kind != 1 && a.mixer_kind != 4)
+                          : a.mixer_kind == 4 || (c.block_kind == 2 ? a.mixer_kind > 1 : (a.mixer_kind == 0) != (c.block_kind == 0)))
+      return fail(lname(i, "mixer: not available in this block form"));
+    L.wsrc = i;
+    if (c.block_kind == 3 && a.weights_of >= 0) {
+      if (a.weights_of >= c.n_layers || lc[a.weights_of].weights_of >= 0) return fail(lname(i, "weights_of must name a layer with weights of its own"));
+      const LayerCfg& o = lc[a.weights_of];
+      if (o.mixer_kind != a.mixer_kind || o.heads != a.heads || o.kv_heads != a.kv_heads || o.dim != a.dim || o.vdim != a.vdim || o.mlp_kind != a.mlp_kind ||
+          o.experts != a.experts || o.expert_ff != a.expert_ff || o.shared_ff != a.shared_ff || o.ssm_heads != a.ssm_heads || o.ssm_vdim != a.ssm_vdim ||
+          o.ssm_state != a.ssm_state || o.ssm_groups != a.ssm_groups || o.conv != a.conv || o.qk_norm != a.qk_norm)
+        return fail(lname(i, "sizes differ from the layer whose weights it uses"));
+      L.wsrc = a.weights_of;
+    }
     if (a.window < 0 || a.softcap < 0.f || a.slope_log2 < 0.f) return fail(lname(i, "mixer: mask.size, softcap and the bias slope must not be negative"));
     if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0) return fail(lname(i, "mixer: sizes must be positive"));
     if (a.mixer_kind == 0) {
@@ -276,8 +319,24 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     } else {
       if (a.kv_heads <= 0 || a.heads % a.kv_heads) return fail(lname(i, "mixer: heads must be a multiple of kv_heads"));
       if (a.dim > 256 || a.vdim > 256) return fail(lname(i, "mixer: head sizes above 256 are outside the kernels' range"));
-      const int nqk = a.mixer_kind == 1 ? a.heads * a.dim + a.kv_heads * a.dim : 2 * a.kv_heads * a.dim;
-      if (a.mixer_kind == 1) {
+      const int nqk = (a.mixer_kind == 1 || a.mixer_kind == 4) ? a.heads * a.dim + a.kv_heads * a.dim : 2 * a.kv_heads * a.dim;
+      if (a.mixer_kind == 4) {
+        if (a.ssm_heads <= 0 || a.ssm_vdim <= 0 || a.ssm_state <= 0 || a.ssm_groups <= 0 || a.ssm_heads % a.ssm_groups || a.conv <= 0 ||
+            a.ssm_norm_groups <= 0 || (a.ssm_heads * a.ssm_vdim) % a.ssm_norm_groups)
+          return fail(lname(i, "mixer: inconsistent state-space branch"));
+        if (a.ssm_state > 256) return fail(lname(i, "mixer: state sizes above 256 are outside the kernels' range"));
+        if (!a.values_are_keys || a.dim != a.vdim) return fail(lname(i, "mixer: the attention branch caches its keys as values (vdim must equal dim)"));
+        const int inner = a.ssm_heads * a.ssm_vdim, C = inner + 2 * a.ssm_groups * a.ssm_state;
+        L.state_off = soff;
+        soff += (int64_t)a.ssm_heads * a.ssm_state * a.ssm_vdim + (int64_t)(a.conv - 1) * C;
+        mx_conv = std::max(mx_conv, C);
+        mx_inner = std::max(mx_inner, inner);
+      }
+      if (c.block_kind == 3) {
+        if (a.qk_norm < 0 || a.qk_norm > 2 || a.q_temp_every < 0 || a.keep_first < 0) return fail(lname(i, "mixer: inconsistent attention options"));
+        if (a.values_are_keys && a.dim != a.vdim) return fail(lname(i, "mixer: values that are keys need vdim == dim"));
+      }
+      if (a.mixer_kind == 1 || a.mixer_kind == 4) {
         if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most dim"));
         if (a.chunk < 0) return fail(lname(i, "mixer: mask.size must be positive"));
         L.owner = i;
@@ -285,6 +344,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
         off += (int64_t)c.page_size * a.kv_heads * (a.dim + a.vdim);
         off = (off + 7) / 8 * 8;  // every layer's block starts 16-byte aligned in both element types
         mx_big = std::max(mx_big, nqk + a.kv_heads * a.vdim + (c.block_kind == 2 ? (a.out_gate ? a.heads * a.vdim : 0) + (c.gated_residual ? c.width : 0) : 0));
+        if (a.mixer_kind == 4) mx_big = std::max(mx_big, nqk + 2 * a.ssm_heads * a.ssm_vdim + 2 * a.ssm_groups * a.ssm_state + a.ssm_heads);
         mx_q = std::max(mx_q, a.heads * a.dim);
       } else {
         if (a.mixer_kind == 2 && a.conv <= 0) return fail(lname(i, "mixer: conv must be positive"));
@@ -301,6 +361,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     if (a.mlp_kind == 1 && a.ff <= 0) return fail(lname(i, "mlp: ff must be positive"));
     if (c.block_kind == 1 && a.mlp_kind == 1) return fail(lname(i, "mlp: the parallel block form has no dense feed-forward"));
     if (c.block_kind == 2 && a.mlp_kind == 2) return fail(lname(i, "mlp: the sandwich block form has no mixture of experts"));
+    if (c.block_kind == 3 && a.mlp_kind == 1) return fail(lname(i, "mlp: the pre-norm block form has no dense feed-forward"));
     if (a.mlp_kind == 2) {
       if (a.experts <= 0 || a.top <= 0 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
           a.top > a.keep * (a.experts / a.groups))
@@ -312,8 +373,9 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
       mx_gu = std::max(mx_gu, 2 * a.ff);
       mx_act = std::max(mx_act, a.ff);
     } else if (a.mlp_kind == 2) {
-      mx_gu = std::max(mx_gu, a.shared_ff);
+      mx_gu = std::max(mx_gu, (c.block_kind == 3 ? 2 : 1) * a.shared_ff);
       mx_act = std::max(mx_act, a.shared_ff);
+      if (a.expert_act == 2 && (!(a.act_limit > 0.f) || (a.shared_ff > 0 && !(a.shared_limit > 0.f)))) return fail(lname(i, "mlp: limit must be positive"));
       mx_e = std::max(mx_e, a.experts);
       mx_top = std::max(mx_top, a.top);
       mx_hid = std::max(mx_hid, a.top * a.expert_ff);
@@ -498,6 +560,57 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
     if (ok) L.got.insert(sub);
     return ok;
   }
+  if (c.block_kind == 3) {
+    // pre-norm block: [q | k | v] (attention) or [q | k | in] (attention beside a state-space branch) stacked into one projection;
+    // expert gate / up rows interleaved; the shared expert's [gate ; up] stacked
+    if (L.wsrc != li) return fail(name + ": layer " + std::to_string(li) + " runs with the weights of layer " + std::to_string(L.wsrc));
+    const int H = a.heads, G = a.kv_heads, mk = a.mixer_kind;
+    const int nq = H * a.dim, nk = G * a.dim, nv = mk == 1 && !a.values_are_keys ? G * a.vdim : 0;
+    const int inner = mk == 4 ? a.ssm_heads * a.ssm_vdim : 0, C = mk == 4 ? inner + 2 * a.ssm_groups * a.ssm_state : 0;
+    const int nin = mk == 4 ? inner + C + a.ssm_heads : 0, nbig = nq + nk + nv + nin;
+    const std::string am = mk == 4 ? "mix.left." : "mix.";  // where the attention's tensors live
+    const int nw = a.qk_norm == 2 ? 0 : a.dim;             // norm weight per head (shared) or over the whole projection
+    if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind && sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
+    else if (sub == am + "q") ok = put(L.qkv, nbig, W, 0, data, nq, name, rows, cols);
+    else if (sub == am + "k") ok = put(L.qkv, nbig, W, nq, data, nk, name, rows, cols);
+    else if (nv && sub == am + "v") ok = put(L.qkv, nbig, W, nq + nk, data, nv, name, rows, cols);
+    else if (a.qk_norm && sub == am + "q.norm") ok = put(L.qn, 1, nw ? nw : nq, 0, data, 1, name, rows, cols);
+    else if (a.qk_norm && sub == am + "k.norm") ok = put(L.kn, 1, nw ? nw : nk, 0, data, 1, name, rows, cols);
+    else if (a.sink_kind == 0 && sub == am + "sink") ok = put(L.sink, 1, H, 0, data, 1, name, rows, cols);
+    else if (sub == am + "o") ok = put(L.o, W, H * a.vdim, 0, data, W, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.in") ok = put(L.qkv, nbig, W, nq + nk, data, nin, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.conv") ok = put(L.conv_w, C, a.conv, 0, data, C, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.conv.b") ok = put(L.conv_b, 1, C, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.A_log") ok = put(L.p0, 1, a.ssm_heads, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.dt_bias") ok = put(L.p1, 1, a.ssm_heads, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.D") ok = put(L.p2, 1, a.ssm_heads, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.norm") ok = put(L.hnorm, 1, inner, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.o") ok = put(L.o2, W, inner, 0, data, W, name, rows, cols);
+    else if (mk == 4 && sub == "mix.left.out") ok = put(L.lout, 1, W, 0, data, 1, name, rows, cols);
+    else if (mk == 4 && sub == "mix.right.out") ok = put(L.rout, 1, W, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub == "mlp.router") ok = put(L.router, a.experts, W, 0, data, a.experts, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub == "mlp.router.b") ok = put(L.corr, 1, a.experts, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.gate") ok = put(L.gate_up, 2 * a.shared_ff, W, 0, data, a.shared_ff, name, rows, cols);
+    else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.up") ok = put(L.gate_up, 2 * a.shared_ff, W, a.shared_ff, data, a.shared_ff, name, rows, cols);
+    else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.down") ok = put(L.s_down, W, a.shared_ff, 0, data, W, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub.rfind("mlp.e", 0) == 0) {
+      const size_t d2 = sub.find('.', 5);
+      if (d2 == std::string::npos) return fail("unknown tensor " + name);
+      const int e = atoi(sub.substr(5, d2 - 5).c_str());
+      const std::string part = sub.substr(d2 + 1);
+      if (e < 0 || e >= a.experts) return fail("expert index out of range: " + name);
+      const int ff = a.expert_ff;
+      if (part == "gate") ok = put_rows(L.e_up, a.experts * 2 * ff, W, e * 2 * ff, 2, data, ff, name, rows, cols);
+      else if (part == "up") ok = put_rows(L.e_up, a.experts * 2 * ff, W, e * 2 * ff + 1, 2, data, ff, name, rows, cols);
+      else if (part == "down") ok = put(L.e_down, a.experts * W, ff, e * W, data, W, name, rows, cols);
+      else return fail("unknown tensor " + name);
+    } else {
+      return fail("unknown tensor " + name + " for the configuration of layer " + std::to_string(li));
+    }
+    if (ok) L.got.insert(sub);
+    return ok;
+  }
   if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "mix.q") ok = put(L.q, a.heads * (a.dim + a.rot_dim), W, 0, data, a.heads * (a.dim + a.rot_dim), name, rows, cols);
@@ -533,10 +646,26 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
 
 // angular frequency of every rotated pair; with YaRN scaling, pairs that turn fewer than `slow` times over the original
 // context are slowed by `factor`, pairs that turn more than `fast` times are kept, a linear ramp over the pair index blends
+// Scaling by wavelength (scaling_kind 1): a pair whose wavelength 2 pi / w is below original / high keeps w, one above original / low
+// turns at w / factor, and between the two the blend is linear in original / wavelength.
 static void rotary_table(const LayerCfg& a, std::vector<float>* f, float* mag) {
   const int half = a.rot_dims / 2;
   f->resize(std::max(half, 1));
   *mag = 1.f;
+  if (a.has_scaling && a.scaling_kind == 1) {
+    const double factor = a.s_factor, orig = a.s_original, high = a.s_fast, low = a.s_slow;
+    for (int i = 0; i < half; ++i) {
+      const double w = std::pow((double)a.rot_base, -2.0 * i / a.rot_dims), wavelength = 2.0 * M_PI / w;
+      double r = w;
+      if (wavelength > orig / low) r = w / factor;
+      else if (!(wavelength < orig / high)) {
+        const double blend = (orig / wavelength - low) / (high - low);
+        r = (1.0 - blend) * w / factor + blend * w;
+      }
+      (*f)[i] = (float)r;
+    }
+    return;
+  }
   double lo = 0, hi = 0;
   if (a.has_scaling) {
     auto pair_of = [&](double turns) { return a.rot_dims * std::log((double)a.s_original / (2.0 * M_PI * turns)) / (2.0 * std::log((double)a.rot_base)); };
@@ -565,7 +694,19 @@ bool Model::finalize() {
     Layer& L = layers[i];
     const LayerCfg& a = L.c;
     std::vector<std::string> need;
-    if (c.block_kind == 0) {
+    if (c.block_kind == 3) {
+      if (L.wsrc == i) {
+        const std::string am = a.mixer_kind == 4 ? "mix.left." : "mix.";
+        need = {"norm1", am + "q", am + "k", am + "o"};
+        if (a.mixer_kind == 1 && !a.values_are_keys) need.push_back(am + "v");
+        if (a.qk_norm) need.insert(need.end(), {am + "q.norm", am + "k.norm"});
+        if (a.sink_kind == 0) need.push_back(am + "sink");
+        if (a.mixer_kind == 4)
+          for (const char* n : {"in", "conv", "conv.b", "A_log", "dt_bias", "D", "norm", "o", "out"}) need.push_back(std::string("mix.right.") + n);
+        if (a.mixer_kind == 4) need.push_back("mix.left.out");
+        if (a.mlp_kind) need.insert(need.end(), {"norm2", "mlp.router.b"});
+      }
+    } else if (c.block_kind == 0) {
       need = {"norm1", "mix.q", "mix.uk", "mix.uv", "mix.sink", "mix.g", "mix.o"};
       if (a.kv_from < 0) need.insert(need.end(), {"mix.dkv", "mix.dkv.norm"});
       if (a.mlp_kind) need.push_back("norm2");
@@ -587,14 +728,14 @@ bool Model::finalize() {
       if (a.mlp_kind == 2) need.push_back("mlp.correction");
     }
     if (a.mlp_kind == 1) need.insert(need.end(), {"mlp.gate", "mlp.up", "mlp.down"});
-    if (a.mlp_kind == 2) {
+    if (a.mlp_kind == 2 && L.wsrc == i) {
       need.push_back("mlp.router");
       for (int e = 0; e < a.experts; ++e) {
-        if (a.expert_act == 1) need.push_back("mlp.e" + std::to_string(e) + ".gate");
+        if (a.expert_act >= 1) need.push_back("mlp.e" + std::to_string(e) + ".gate");
         need.push_back("mlp.e" + std::to_string(e) + ".up");
         need.push_back("mlp.e" + std::to_string(e) + ".down");
       }
-      if (a.shared_ff > 0) need.insert(need.end(), {"mlp.shared.up", "mlp.shared.down", "mlp.shared.sg"});
+      if (a.shared_ff > 0) need.insert(need.end(), {"mlp.shared.up", "mlp.shared.down", c.block_kind == 3 ? "mlp.shared.gate" : "mlp.shared.sg"});
     }
     for (auto& n : need)
       if (!L.got.count(n)) return fail("tensor " + lname(i, n.c_str()) + " is missing");
@@ -604,7 +745,11 @@ bool Model::finalize() {
       if (a.mixer_kind >= 2 && (!to_f32(L.p0, &L.p0_32) || !to_f32(L.p1, &L.p1_32))) return false;
       if (a.mixer_kind != 1) continue;  // only attention rotates
     }
-    if (c.block_kind == 2 && a.rot_dims == 0) continue;  // nothing rotates
+    if (c.block_kind == 3 && L.wsrc == i) {
+      if (a.mlp_kind == 2 && !to_f32(L.corr, &L.corr32)) return false;
+      if (a.mixer_kind == 4 && (!to_f32(L.p0, &L.p0_32) || !to_f32(L.p1, &L.p1_32) || !to_f32(L.p2, &L.p2_32))) return false;
+    }
+    if (c.block_kind >= 2 && a.rot_dims == 0) continue;  // nothing rotates
     std::vector<float> f;
     rotary_table(a, &f, &L.mag);
     if (!L.freq.alloc_zeros(f.size() * 4) || !cu(cudaMemcpy(L.freq.ptr, f.data(), f.size() * 4, cudaMemcpyHostToDevice), "rotary table"))
@@ -644,6 +789,9 @@ bool Model::ensure_scratch(int T, int R) {
       ok = h32.alloc_uninit(n * W * 4) && big.alloc_uninit(n * std::max(mx_big, 1) * es) && convo.alloc_uninit(n * std::max(mx_conv, 1) * es) &&
            zs.alloc_uninit(n * std::max(mx_small, 1) * 4) && orec.alloc_uninit(n * std::max(mx_ao, 1) * 4) && den.alloc_uninit(n * std::max(mx_h, 1) * 4);
     if (ok && c.block_kind == 2) ok = big.alloc_uninit(n * std::max(mx_big, 1) * es) && rgbuf.alloc_uninit(n * W * es);
+    if (ok && c.block_kind == 3)
+      ok = h32.alloc_uninit(n * W * 4) && big.alloc_uninit(n * std::max(mx_big, 1) * es) && convo.alloc_uninit(n * std::max(mx_conv, 1) * es) &&
+           orec.alloc_uninit(n * std::max(mx_inner, 1) * 4) && ao2.alloc_uninit(n * std::max(mx_inner, 1) * es) && mix2.alloc_uninit(n * W * es);
     if (ok && !c.f32 && (int)n >= kGroupedMinTokens) {  // bucketed experts for prompt portions
       long ws = 0;
       for (auto& L : layers)
@@ -754,7 +902,7 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
       if (!skinny(L.s_gate, (float*)sgl.ptr, T, "shared expert gate")) return false;
       shared = sh.ptr;
     }
-    if (!run_experts(L, T, shared)) return false;
+    if (!run_experts(L, T, shared, (const float*)sgl.ptr)) return false;
     if (!rc(k.pk_res32_offset_norm_add(yf.ptr, 1, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
   }
   if (keep_trail)
@@ -763,20 +911,22 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
 }
 
 // routed experts of one layer for the tokens in xa: router logits are in zs (block 1) or z (block 0); result in yf (fp32)
-bool Model::run_experts(Layer& L, int T, const void* shared) {
+bool Model::run_experts(const Layer& L, int T, const void* shared, const float* shared_gate) {
   const LayerCfg& a = L.c;
   const int W = c.width, f32 = c.f32;
   // many tokens: rows bucketed by expert on the tensor cores; a few tokens: per token, reading only the chosen experts' weights
   int grouped = -2;
   if (!f32 && T >= kGroupedMinTokens && moe_ws.ptr) {
-    grouped = k.pk_moe_grouped_act(xa.ptr, L.e_up.d.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr,
-                                   (float*)yf.ptr, moe_ws.ptr, T, a.top, a.experts, W, a.expert_ff, a.expert_act, st);
+    grouped = k.pk_moe_grouped_act_p(xa.ptr, L.e_up.d.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, shared_gate,
+                                     (float*)yf.ptr, moe_ws.ptr, T, a.top, a.experts, W, a.expert_ff, a.expert_act, a.act_limit, a.act_slope, st);
     if (grouped != -2 && !rc(grouped, "experts (grouped)")) return false;
   }
-  if (grouped == -2 && !rc(k.pk_moe_up_act(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, a.expert_act, f32, st), "experts up"))
+  if (grouped == -2 && !rc(k.pk_moe_up_act_p(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, a.expert_act, a.act_limit,
+                                             a.act_slope, f32, st),
+                           "experts up"))
     return false;
   if (grouped == -2 &&
-      !rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
+      !rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, shared_gate, (float*)yf.ptr, T,
                                 a.top, W, a.expert_ff, f32, st),
           "experts down"))
     return false;
@@ -835,7 +985,7 @@ bool Model::run_parallel_layer(int li, int T, const int* M, int n) {
                                 a.keep, a.route_scale, a.router_kind, a.router_kind == 1 ? 2 : 1, a.router_kind == 1 ? 0 : 1, st),
             "router top-k"))
       return false;
-    if (!run_experts(L, T, nullptr)) return false;
+    if (!run_experts(L, T, nullptr, nullptr)) return false;
   }
   return true;
 }
@@ -979,6 +1129,96 @@ bool Model::run_sandwich_layer(int li, int T, int max_kv, const int* M) {
   return true;
 }
 
+// Pre-norm block: on entry xa (and h32, unrounded) hold rms(x) * norm1 of this layer; on exit x holds the layer's result and xa / h32
+// the next layer's pre-norm (nothing after the last layer).  Weights come from layer `wsrc`, cache and state are this layer's own.
+bool Model::run_prenorm_layer(int li, int T, int max_kv, const int* M, int n) {
+  Layer& L = layers[li];
+  const Layer& Wt = layers[L.wsrc];
+  const LayerCfg& a = L.c;
+  const int W = c.width, f32 = c.f32, H = a.heads, G = a.kv_heads, mk = a.mixer_kind;
+  const int *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_slot = M + 3 * T + n, *d_row0 = M + 3 * T + 2 * n, *d_len = M + 3 * T + 3 * n;
+  const int* d_pages = M + pages_at;
+  char* pool_base = (char*)cache.ptr + (size_t)L.cache_off * es;
+  const int nq = H * a.dim, nk = G * a.dim, nv = mk == 1 && !a.values_are_keys ? G * a.vdim : 0;
+  const int inner = mk == 4 ? a.ssm_heads * a.ssm_vdim : 0, C = mk == 4 ? inner + 2 * a.ssm_groups * a.ssm_state : 0;
+  const int nin = mk == 4 ? inner + C + a.ssm_heads : 0, nbig = nq + nk + nv + nin;
+  const Layer* next = li + 1 < c.n_layers ? &layers[layers[li + 1].wsrc] : nullptr;
+  const void* after_mixer = a.mlp_kind ? Wt.norm2.d.ptr : next ? next->norm1.d.ptr : nullptr;
+  // ---- mixer: one stacked projection, then the attention (both mixers have one)
+  if (!lin(Wt.qkv, xa.ptr, big.ptr, T)) return false;
+  pk_qk_prep prep{};
+  prep.norm_kind = a.qk_norm;
+  prep.q_weight = Wt.qn.d.ptr;
+  prep.k_weight = Wt.kn.d.ptr;
+  prep.eps = c.eps;
+  prep.temp_coef = a.q_temp_coef;
+  prep.temp_every = a.q_temp_every;
+  prep.values_are_keys = a.values_are_keys;
+  if (!rc(k.pk_gqa_norm_append(big.ptr, nbig, d_pos, d_req, d_poff, d_pages, q.ptr, pool_base, page_stride, c.page_size, H, G, a.dim, a.vdim, a.rot_dims,
+                               a.rot_interleaved, (const float*)Wt.freq.ptr, Wt.mag, &prep, T, f32, st),
+          "q / k norm + cache append"))
+    return false;
+  pk_attn_extra ex{};
+  ex.window = a.window;
+  ex.keep_first = a.keep_first;
+  ex.max_kv_len = max_kv;
+  if (!rc(k.pk_gqa_attention_ex(q.ptr, pool_base, a.sink_kind == 0 ? Wt.sink.d.ptr : nullptr, d_pos, d_req, d_poff, d_pages, ao.ptr, page_stride, c.page_size,
+                                T, H, G, a.dim, a.vdim, a.scale, a.chunk, &ex, f32, st),
+          "attention"))
+    return false;
+  if (!lin(Wt.o, ao.ptr, mix.ptr, T)) return false;
+  if (mk == 4) {
+    // ---- state-space branch on the rows [z | x B C | dt] of the same projection
+    const int in_off = nq + nk, Hs = a.ssm_heads, N = a.ssm_state, P = a.ssm_vdim, gs = inner / a.ssm_norm_groups;
+    float* slot0 = (float*)state.ptr + L.state_off;
+    if (!rc(k.pk_causal_conv_silu_bias((const char*)big.ptr + (size_t)(in_off + inner) * es, nbig, Wt.conv_w.d.ptr, Wt.conv_b.d.ptr,
+                                       slot0 + (size_t)Hs * N * P, slot_stride, d_req, d_slot, d_row0, d_len, convo.ptr, C, C, a.conv, T, n, f32, st),
+            "short convolution"))
+      return false;
+    if (!rc(k.pk_ssd_seq(convo.ptr, C, 0, inner, inner + a.ssm_groups * N, big.ptr, nbig, in_off + inner + C, (const float*)Wt.p0_32.ptr,
+                         (const float*)Wt.p1_32.ptr, (const float*)Wt.p2_32.ptr, slot0, slot_stride, d_slot, d_row0, d_len, (float*)orec.ptr, Hs,
+                         a.ssm_groups, N, P, n, f32, st),
+            "state-space recurrence"))
+      return false;
+    if (!rc(k.pk_head_norm_gate((const float*)orec.ptr, nullptr, Wt.hnorm.d.ptr, gs, big.ptr, nbig, in_off, ao2.ptr, T, a.ssm_norm_groups, gs, c.eps, 2, f32,
+                                st),
+            "gated read-out norm"))
+      return false;
+    if (!lin(Wt.o2, ao2.ptr, mix2.ptr, T)) return false;
+    if (!rc(k.pk_res32_branches_add_norm(mix.ptr, 0, Wt.lout.d.ptr, mix2.ptr, Wt.rout.d.ptr, 0.5f, (float*)x.ptr, after_mixer, xa.ptr, (float*)h32.ptr, W,
+                                         c.eps, T, f32, st),
+            "mixer result: branch norms, residual, next norm"))
+      return false;
+  } else if (!rc(k.pk_res32_branches_add_norm(mix.ptr, 0, nullptr, nullptr, nullptr, 1.f, (float*)x.ptr, after_mixer, xa.ptr, (float*)h32.ptr, W, c.eps, T,
+                                              f32, st),
+                 "mixer result: residual, next norm")) {
+    return false;
+  }
+  // ---- feed-forward: routed experts plus an ungated shared expert of the same form
+  if (a.mlp_kind == 2) {
+    if (!skinny(Wt.router, (float*)z.ptr, T, "router", (const float*)h32.ptr)) return false;
+    if (!rc(k.pk_router_topk_logits((const float*)z.ptr, a.experts, (const float*)Wt.corr32.ptr, (int*)ids.ptr, (float*)wts.ptr, T, a.experts, a.top,
+                                    a.route_scale, st),
+            "router top-k"))
+      return false;
+    const void* shared = nullptr;
+    if (a.shared_ff > 0) {
+      if (!lin(Wt.gate_up, xa.ptr, gu.ptr, T)) return false;
+      if (!rc(k.pk_act_clamped(gu.ptr, act.ptr, a.shared_ff, T, a.shared_limit, a.act_slope, f32, st), "shared expert activation")) return false;
+      if (!lin(Wt.s_down, act.ptr, sh.ptr, T)) return false;
+      shared = sh.ptr;
+    }
+    if (!run_experts(Wt, T, shared, nullptr)) return false;
+    if (!rc(k.pk_res32_branches_add_norm(yf.ptr, 1, nullptr, nullptr, nullptr, 1.f, (float*)x.ptr, next ? next->norm1.d.ptr : nullptr, xa.ptr,
+                                         (float*)h32.ptr, W, c.eps, T, f32, st),
+            "feed-forward result: residual, next norm"))
+      return false;
+  }
+  if (keep_trail)
+    return cu(cudaMemcpyAsync((char*)trail.ptr + (size_t)li * T * W * 4, x.ptr, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st), "trail copy");
+  return true;
+}
+
 // everything between the metadata upload and the final synchronisation: launches only (no allocation, no synchronisation)
 bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
   const int* M = meta_d.i32();
@@ -989,6 +1229,13 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
     if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, W, T, c.f32, st), "embedding")) return false;
     for (int li = 0; li < c.n_layers; ++li)
       if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
+  } else if (c.block_kind == 3) {
+    if (!rc(k.pk_res32_embed_scaled_norm(embed.d.ptr, d_tok, c.embed_scale, (float*)x.ptr, layers[layers[0].wsrc].norm1.d.ptr, xa.ptr, (float*)h32.ptr, W, c.eps,
+                                         T, c.f32, st),
+            "embedding"))
+      return false;
+    for (int li = 0; li < c.n_layers; ++li)
+      if (!run_prenorm_layer(li, T, max_kv, M, n)) return false;
   } else if (c.block_kind == 2) {
     if (!rc(k.pk_res32_embed_gnorm(embed.d.ptr, d_tok, embed_norm.d.ptr, (float*)x.ptr, layers[0].norm1.d.ptr, xa.ptr, W, c.norm_groups, c.eps, T, c.f32, st),
             "embedding"))
@@ -1014,8 +1261,10 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
   if (n_rows > 0) {
     if (c.block_kind == 0) {
       if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, n_rows, c.eps, c.f32, st), "final norm")) return false;
-    } else if (c.block_kind == 2) {
-      if (!rc(k.pk_res32_gnorm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, c.norm_groups, c.eps, n_rows, c.f32, st), "final norm")) return false;
+    } else if (c.block_kind >= 2) {  // the pre-norm block form's last norm is the same norm with one group
+      if (!rc(k.pk_res32_gnorm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, c.block_kind == 2 ? c.norm_groups : 1, c.eps, n_rows, c.f32, st),
+              "final norm"))
+        return false;
     } else if (!rc(k.pk_res32_dyt_rows((const float*)x.ptr, d_rows, (const float*)final_alpha32.ptr, final_norm.d.ptr, final_b.d.ptr, xr.ptr, W, n_rows, c.f32,
                                        st),
                    "final norm")) {
@@ -1023,9 +1272,13 @@ bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
     }
     if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
     const float ls = c.block_kind >= 1 ? c.logit_scale : 1.f;
-    if (!rc(k.pk_scale_to_f32(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, st), "logits")) return false;
+    if (c.block_kind == 3) {
+      if (!rc(k.pk_logits_scale_cap(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, c.logit_softcap, st), "logits")) return false;
+    } else if (!rc(k.pk_scale_to_f32(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, st), "logits")) {
+      return false;
+    }
     if (want_sample) {
-      if (c.f32 || ls != 1.f) {  // the final (scaled) logits exist in fp32 only: greedy token of every row from those
+      if (c.f32 || ls != 1.f || c.block_kind == 3) {  // the final (scaled) logits exist in fp32 only: greedy token of every row from those
         if (!rc(k.pk_top1_rows_f32((const float*)logits_f.ptr, sampled_d.i32(), n_rows, c.vocab, st), "greedy token")) return false;
       } else {
         const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;

@@ -113,7 +113,15 @@ i64l = C.c_long
 
 class AttnExtra(C.Structure):
     """pk_attn_extra: options of pk_gqa_attention_ex (a zero / NULL field switches its option off)."""
-    _fields_ = [("window", i32), ("softcap", f32), ("slope_log2", f32), ("gate", vp), ("gate_ld", i64l), ("max_kv_len", i32)]
+    _fields_ = [("window", i32), ("softcap", f32), ("slope_log2", f32), ("gate", vp), ("gate_ld", i64l), ("max_kv_len", i32),
+                ("keep_first", i32)]
+
+
+class QkPrep(C.Structure):
+    """pk_qk_prep: what pk_gqa_norm_append does to q and k (norm per head or over the whole projection, the query's factor that grows with
+    the logarithm of the position, keys cached in the place of values)."""
+    _fields_ = [("norm_kind", i32), ("q_weight", vp), ("k_weight", vp), ("eps", f32), ("temp_coef", f32), ("temp_every", i32),
+                ("values_are_keys", i32)]
 
 
 RES32_SIGNATURES = {
@@ -157,6 +165,17 @@ RES32_SIGNATURES = {
     "pk_rope_slice_ex": (i32, [vp, vp, vp, vp, f32] + [i32] * 10 + [vp]),
     "pk_latent_kv_append_ex": (i32, [vp] * 7 + [i64l, i32, i32, i32, i32, i32, vp, f32, f32, i32, i32, vp]),
     "pk_latent_attention_ex": (i32, [vp] * 8 + [i64l, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp]),
+    # pre-norm blocks, normed queries / keys, state-space layers, clamped gated experts
+    "pk_res32_embed_scaled_norm": (i32, [vp, vp, f32, vp, vp, vp, vp, i32, f32, i32, i32, vp]),
+    "pk_res32_branches_add_norm": (i32, [vp, i32, vp, vp, vp, f32, vp, vp, vp, vp, i32, f32, i32, i32, vp]),
+    "pk_logits_scale_cap": (i32, [vp, i32, vp, i64l, f32, f32, vp]),
+    "pk_act_clamped": (i32, [vp, vp, i32, i32, f32, f32, i32, vp]),
+    "pk_gqa_norm_append": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, i64l] + [i32] * 7 + [vp, f32, C.POINTER(QkPrep), i32, i32, vp]),
+    "pk_causal_conv_silu_bias": (i32, [vp, i32, vp, vp, vp, i64l, vp, vp, vp, vp, vp] + [i32] * 6 + [vp]),
+    "pk_ssd_seq": (i32, [vp, i32, i32, i32, i32, vp, i32, i32, vp, vp, vp, vp, i64l, vp, vp, vp, vp] + [i32] * 6 + [vp]),
+    "pk_router_topk_logits": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, f32, vp]),
+    "pk_moe_up_act_p": (i32, [vp, vp, vp, vp] + [i32] * 5 + [f32, f32, i32, vp]),
+    "pk_moe_grouped_act_p": (i32, [vp] * 9 + [i32] * 6 + [f32, f32, vp]),
 }
 
 

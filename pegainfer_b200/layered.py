@@ -24,14 +24,18 @@ class LayerCfg(C.Structure):
                [("route_scale", C.c_float), ("expert_ff", C.c_int), ("shared_ff", C.c_int)] + \
                [(n, C.c_int) for n in ("mixer_kind", "kv_heads", "chunk", "conv", "rot_interleaved")] + [("gate_cap", C.c_float)] + \
                [(n, C.c_int) for n in ("router_kind", "expert_act", "window")] + [("softcap", C.c_float), ("slope_log2", C.c_float)] + \
-               [(n, C.c_int) for n in ("value_norm", "sink_kind", "out_gate", "proj_bias")]
+               [(n, C.c_int) for n in ("value_norm", "sink_kind", "out_gate", "proj_bias", "keep_first", "qk_norm")] + \
+               [("q_temp_coef", C.c_float)] + \
+               [(n, C.c_int) for n in ("q_temp_every", "values_are_keys", "scaling_kind", "ssm_heads", "ssm_vdim", "ssm_state", "ssm_groups",
+                                       "ssm_norm_groups")] + \
+               [(n, C.c_float) for n in ("act_limit", "act_slope", "shared_limit")] + [("weights_of", C.c_int)]
 
 
 class ModelCfg(C.Structure):
     _fields_ = [("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("eps", C.c_float)] + \
                [(n, C.c_int) for n in ("f32", "page_size", "num_pages", "max_requests", "device", "enable_pdl", "block_kind")] + \
                [("embed_scale", C.c_float), ("logit_scale", C.c_float), ("norm_groups", C.c_int), ("residual_mult", C.c_float),
-                ("gated_residual", C.c_int)]
+                ("gated_residual", C.c_int), ("logit_softcap", C.c_float)]
 
 
 def typed_host():
@@ -108,7 +112,7 @@ class LayeredModel:
         mc = self.model_struct(cfg, ModelCfg(vocab=cfg.vocab, width=cfg.width, n_layers=len(cfg.layers), eps=cfg.eps, f32=f32, page_size=PAGE_SIZE,
                                              num_pages=pages_for(max_tokens) if max_tokens > 0 else 0, max_requests=max_requests, device=device_ordinal,
                                              enable_pdl=int(enable_pdl), block_kind=0, embed_scale=1.0, logit_scale=1.0, norm_groups=1,
-                                             residual_mult=1.0, gated_residual=0))
+                                             residual_mult=1.0, gated_residual=0, logit_softcap=0.0))
         torch.cuda.set_device(device_ordinal)
         self._m = self._h.pv_create(C.byref(mc), lcs, (kernel_lib or ffi.KERNEL_LIB_PATH).encode())
         if not self._m:

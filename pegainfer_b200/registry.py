@@ -28,6 +28,11 @@ def _load_nagosun(path, dtype, max_tokens, max_requests, **kw):
     return NagosunModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
 
 
+def _load_goguzen(path, dtype, max_tokens, max_requests, **kw):
+    from .goguzen import GoguzenModel
+    return GoguzenModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
+
+
 def _load_qwen3(path, dtype, max_tokens, max_requests, **kw):
     from .config import PAGE_SIZE
     from .model import ModelRuntimeConfig, Qwen3Model
@@ -42,11 +47,12 @@ ARCHITECTURES = {
     "Vamadra": _load_vamadra,
     "Risolorn": _load_risolorn,
     "Nagosun": _load_nagosun,
+    "Goguzen": _load_goguzen,
     "Qwen3ForCausalLM": _load_qwen3,
     "qwen3": _load_qwen3,
 }
 # designs whose kernels run with every product in fp32 as well
-FLOAT32_CAPABLE = {"Vamadra", "Risolorn", "Nagosun"}
+FLOAT32_CAPABLE = {"Vamadra", "Risolorn", "Nagosun", "Goguzen"}
 
 
 def architecture_of(model_path: str) -> str:
