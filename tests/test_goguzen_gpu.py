@@ -1,0 +1,895 @@
+"""Goguzen on the GPU against the plain oracle (oracle/goguzen_oracle.py): mechanisms alone through the C ABI or as one-layer
+models, then the model through its own step / engine / generate entry points -- whole prompts, token-by-token decoding,
+portions down to two tokens, unequal batches, reused pages and state slots, keys far back, at page borders, on both sides of
+a window's edge and of the kept first positions, the first tokens, long decoding, layers that share weights, greedy generation.
+
+Configurations and weights are made here (small, random, seeded).  float32 runs are held to 2e-4 of the logits' spread
+(against the oracle in fp64), bfloat16 runs to rounding noise.  Where random weights would blur a fault (one far key among
+hundreds, the sink, a window's edge) the inputs are built so that a single score dominates.
+"""
+import ctypes as C
+import math
+import random
+
+import pytest
+import torch
+
+from oracle import goguzen_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32, F64, BF16 = torch.float32, torch.float64, torch.bfloat16
+RESCALE = {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 40}
+
+
+# ------------------------------------------------------------------ configurations (none is a real checkpoint's)
+def att(heads, kv_heads, dim, vdim, size=0, keep=0, rot_dims=None, scaling=True, base=10000.0, scale=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+    if size:
+        m["mask"] = {"size": size, "keep_first": keep}
+    dims = dim if rot_dims is None else rot_dims
+    if dims:
+        m["rot"] = {"dims": dims, "base": base}
+        if scaling:
+            m["rot"]["scaling"] = dict(RESCALE)
+    return {"type": "attention", "mixer": m}
+
+
+def par(heads, kv_heads, dim, s_heads, s_vdim, state, groups, conv, norm_groups, coef=0.4, every=16, scale=None):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale if scale is not None else 1.0 / math.sqrt(dim),
+            "q_temp": {"coef": coef, "every": every}}
+    right = {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+    return {"type": "parallel", "mixer": {"left": left, "right": right}}
+
+
+def moe(experts, top, ff, limit, shared_ff=0, shared_limit=0.0):
+    d = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+    if shared_ff:
+        d["shared"] = {"ff": shared_ff, "limit": shared_limit}
+    return d
+
+
+def model_cfg(layers, vocab=211, width=88, eps=1e-5, embed=3.0, logit=0.7, cap=12.0):
+    """layers: (mixer entry, mlp) or an int j for a layer that runs with layer j's weights"""
+    out = []
+    for l in layers:
+        out.append(None if isinstance(l, int) else dict(l[0], mlp=l[1]))
+    for i, l in enumerate(layers):
+        if isinstance(l, int):
+            out[i] = dict(out[l], weights_of=l)
+    return {"architecture": "Goguzen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed}, "logit_scale": logit,
+            "logit_softcap": cap, "layers": out}
+
+
+def cfg_general():
+    """All sizes differ from each other; both mixers; a layer that borrows weights BEFORE its owner runs and one after; a layer without
+    feed-forward; the bf16 attention of layer 1 takes the tensor-core kernel (window and kept first keys), layer 3 the generic one."""
+    return model_cfg([2,
+                      (att(4, 2, 64, 64, 37, 5, rot_dims=16), moe(6, 3, 40, 2.0, 24, 1.5)),
+                      (par(6, 2, 32, 5, 24, 20, 1, 4, 3), moe(8, 2, 56, 1.2, 40, 0.9)),
+                      (att(3, 1, 24, 40, 21, 9, scaling=False, base=500.0), None),
+                      1])
+
+
+def cfg_edges():
+    """Values that often coincide or equal one are made to differ or to be one: one head, kv_heads == heads, top 1, no shared expert,
+    one- and two-tap convolutions, one norm group and as many as heads, a window of two tokens, no kept tokens, more kept tokens than
+    the window is wide, a query factor that changes at every position, widths that are no multiple of 8, no soft cap."""
+    return model_cfg([(att(1, 1, 12, 20, 2, 0, rot_dims=8), moe(4, 1, 28, 0.8)),
+                      (par(1, 1, 12, 2, 10, 6, 2, 1, 1, coef=1.3, every=1), None),
+                      (att(2, 2, 20, 12, 6, 11, rot_dims=0), moe(5, 5, 20, 3.0, 12, 0.5)),
+                      (par(3, 3, 8, 4, 9, 36, 4, 2, 4, coef=0.2, every=7), moe(4, 2, 12, 1.0, 52, 2.0))], vocab=97, width=52, eps=1e-6, embed=0.5,
+                     logit=1.5, cap=0.0)
+
+
+def cfg_wide():
+    """head and state sizes the 128-wide register tiles take; window = a multiple of the page size; a borrowed layer at the end"""
+    return model_cfg([(att(4, 1, 128, 128, 64, 16), moe(4, 2, 64, 1.0, 64, 1.0)), (par(2, 1, 96, 2, 64, 128, 1, 3, 2), None), 1],
+                     vocab=128, width=64)
+
+
+def cfg_no_window():
+    """attention without a mask block (plain causal) and without rotation beside a windowed one"""
+    a = att(2, 1, 16, 16, rot_dims=0)
+    return model_cfg([(a, moe(4, 2, 24, 1.0, 16, 1.0)), (att(4, 2, 8, 12, 11, 3), None)], vocab=80, width=40)
+
+
+CONFIGS = {"general": cfg_general, "edges": cfg_edges, "wide": cfg_wide, "no_window": cfg_no_window}
+
+
+def make_weights(cfg, seed, sharp=1.0):
+    """bf16 checkpoint; `sharp` scales the weights of the query norms (the norm removes any scale of the projection itself) so that
+    the softmax is peaked on single keys."""
+    from pegainfer_b200.goguzen import GoguzenConfig, weight_shapes
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in weight_shapes(GoguzenConfig.from_dict(cfg)).items():
+        leaf = name.rsplit(".", 1)[-1]
+        rn = lambda s=1.0: s * torch.randn(shape, generator=g)  # noqa: E731
+        if name.endswith("q.norm"):
+            t = sharp * (1.0 + 0.2 * rn())
+        elif leaf in ("norm", "norm1", "norm2", "out"):
+            t = 1.0 + 0.2 * rn()
+        elif leaf == "conv":
+            t = rn(0.6)
+        elif leaf == "A_log":
+            t = rn(0.7) - 1.0
+        elif leaf == "D":
+            t = 1.0 + 0.3 * rn()
+        elif leaf == "sink":
+            t = rn(1.5)
+        elif len(shape) == 1:
+            t = rn(0.4)
+        elif name == "embed":
+            t = rn()
+        else:
+            t = rn() / math.sqrt(shape[1])
+            if leaf == "router":
+                t = t * 3.0
+        w[name] = t.to(BF16)
+    return w
+
+
+def build(cfg, w, dtype, max_tokens=1024, max_requests=4):
+    from pegainfer_b200.goguzen import GoguzenConfig, GoguzenModel
+    return GoguzenModel(GoguzenConfig.from_dict(cfg), w, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests)
+
+
+def row_errors(got, want):
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
+
+
+def close(got, want, dtype):
+    """float32: every row within 2e-4 of the logits' spread.  bfloat16: rounding noise only -- half of the rows within 4 %, 85 in
+    100 within 10 % (a routing decision that rounding flips moves single rows; a wrong key, mask, state or page shows in the
+    float32 run of the same test)."""
+    e = row_errors(got, want.to(F32))
+    if dtype == F32:
+        return e.max().item() < 2e-4
+    return e.median().item() < 0.04 and e.quantile(0.85).item() < 0.10
+
+
+# sharper attention than the scale alone gives: in float32 a lost or shifted key then moves the logits well above the bound
+SHARP = {F32: 4.0, BF16: 1.5}
+
+
+def tokens_for(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def oracle_logits(cfg, w, toks, trail=None):
+    return O.forward(cfg, w, toks, trail, dtype=F64)
+
+
+# ------------------------------------------------------------------ kernels alone
+@pytest.fixture(scope="module")
+def lib():
+    from pegainfer_b200 import ffi
+    ffi.lib().cublas_init()
+    return ffi.lib()
+
+
+def dev(t, dtype):
+    return t.to(dtype).cuda().contiguous()
+
+
+def i32(xs):
+    return torch.tensor(xs, dtype=torch.int32, device="cuda")
+
+
+class Hold:
+    """ptr(t) returns t's device address and keeps t alive until the launches that read it are done."""
+
+    def __init__(self):
+        self.kept = []
+
+    def __call__(self, t):
+        self.kept.append(t)
+        return t.data_ptr()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("W", [52, 64, 13000])
+def test_residual_step_with_branch_norms(lib, dtype, W):
+    """x += mult * (rms(a) wa + rms(b) wb), then the next norm; also with one branch, an unnormed fp32 branch and no next norm"""
+    P = Hold()
+    T, eps = 5, 1e-5
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    x, ya, yb, yf = rnd(T, W), rnd(T, W).to(dtype).to(F32), (3 * rnd(T, W)).to(dtype).to(F32), rnd(T, W)
+    wa, wb, wn = [(1 + 0.3 * rnd(W)).to(dtype) for _ in range(3)]
+    f32 = int(dtype == F32)
+    for case in ("two", "one", "plain_f32", "last"):
+        xd, h, h32 = x.cuda(), torch.zeros(T, W, dtype=dtype, device="cuda"), torch.zeros(T, W, device="cuda")
+        if case == "two":
+            rc = lib.pk_res32_branches_add_norm(P(dev(ya, dtype)), 0, P(wa.cuda()), P(dev(yb, dtype)), P(wb.cuda()), 0.5, xd.data_ptr(), P(wn.cuda()),
+                                                h.data_ptr(), h32.data_ptr(), W, eps, T, f32, None)
+            xs = x + 0.5 * (O.rms(ya, eps) * wa.float() + O.rms(yb, eps) * wb.float())
+        elif case == "one":
+            rc = lib.pk_res32_branches_add_norm(P(dev(ya, dtype)), 0, None, None, None, 1.0, xd.data_ptr(), P(wn.cuda()), h.data_ptr(), None, W, eps, T,
+                                                f32, None)
+            xs = x + ya
+        elif case == "plain_f32":
+            rc = lib.pk_res32_branches_add_norm(P(yf.cuda()), 1, None, None, None, 1.0, xd.data_ptr(), P(wn.cuda()), h.data_ptr(), h32.data_ptr(), W, eps,
+                                                T, f32, None)
+            xs = x + yf
+        else:
+            rc = lib.pk_res32_branches_add_norm(P(yf.cuda()), 1, None, None, None, 1.0, xd.data_ptr(), None, None, None, W, eps, T, f32, None)
+            xs = x + yf
+        torch.cuda.synchronize()
+        assert rc == 0, case
+        assert torch.allclose(xd.cpu(), xs, atol=3e-6), case
+        if case != "last":
+            want = O.rms(xs, eps) * wn.float()
+            assert torch.allclose(h.float().cpu(), want, atol=3e-6 if dtype == F32 else 3e-2), case
+            if case != "one":
+                assert torch.allclose(h32.cpu(), want, atol=3e-6), case
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_scaled_embedding_with_first_norm_and_capped_logits(lib, dtype):
+    P = Hold()
+    T, W, V, eps = 6, 44, 30, 1e-6
+    g = torch.Generator().manual_seed(2)
+    emb, wn = torch.randn(V, W, generator=g).to(dtype), (1 + 0.3 * torch.randn(W, generator=g)).to(dtype)
+    ids = [3, 29, 0, 3, 17, 8]
+    x, h, h32 = torch.zeros(T, W, device="cuda"), torch.zeros(T, W, dtype=dtype, device="cuda"), torch.zeros(T, W, device="cuda")
+    assert lib.pk_res32_embed_scaled_norm(P(emb.cuda()), P(i32(ids)), 2.5, x.data_ptr(), P(wn.cuda()), h.data_ptr(), h32.data_ptr(), W, eps, T,
+                                          int(dtype == F32), None) == 0
+    z = (4 * torch.randn(T, V, generator=g)).to(dtype)
+    out, out0 = torch.zeros(T, V, device="cuda"), torch.zeros(T, V, device="cuda")
+    assert lib.pk_logits_scale_cap(P(z.cuda()), int(dtype == F32), out.data_ptr(), T * V, 0.7, 1.9, None) == 0
+    assert lib.pk_logits_scale_cap(P(z.cuda()), int(dtype == F32), out0.data_ptr(), T * V, 0.7, 0.0, None) == 0
+    torch.cuda.synchronize()
+    xs = emb.float()[ids] * 2.5
+    assert torch.allclose(x.cpu(), xs, atol=1e-6)
+    assert torch.allclose(h32.cpu(), O.rms(xs, eps) * wn.float(), atol=3e-6)
+    assert torch.allclose(out.cpu(), 1.9 * torch.tanh(z.float() * 0.7 / 1.9), atol=2e-6)
+    assert torch.allclose(out0.cpu(), z.float() * 0.7, atol=1e-6)
+
+
+def paged(req_lens, page_size, shuffle_seed=0):
+    """A page table with pages handed out in a scrambled order: (pages flat, page_off per request, number of pages)."""
+    need = [(n + page_size - 1) // page_size for n in req_lens]
+    order = torch.randperm(sum(need) + 3, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    pages, off, k = [], [], 0
+    for n in need:
+        off.append(len(pages))
+        pages += order[k:k + n]
+        k += n
+    return pages, off, sum(need) + 3
+
+
+def run_attention(lib, dtype, mx, kind, qkv, qw, kw, sink, starts, lens, eps=1e-5, ps=16, max_kv=0):
+    """q / k norm + rotation + cache append + attention for a step whose request r brings positions starts[r] .. lens[r] - 1 (earlier
+    positions were appended by a first call).  kind "attention": rows [q | k | v], norm over the whole projection, rotation, window with
+    kept first keys; kind "left": rows [q | k], values = keys as projected, norm per head, query factor.  Returns [T, H * vdim]."""
+    from pegainfer_b200.ffi import AttnExtra, QkPrep
+    P = Hold()
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    left = kind == "left"
+    n_all = H * D + G * D + (0 if left else G * Dv)
+    pages, off, n_pages = paged(lens, ps, shuffle_seed=5)
+    stride = ps * G * (D + Dv) + 24
+    cache = torch.zeros(n_pages, stride, dtype=dtype, device="cuda")
+    rot = mx.get("rot")
+    freq = O.rescaled_frequencies(rot).to(F32).cuda() if rot else None
+    f32 = int(dtype == F32)
+    mask, qt = mx.get("mask") or {}, mx.get("q_temp") or {}
+    prep = QkPrep(norm_kind=1 if left else 2, q_weight=P(dev(qw, dtype)), k_weight=P(dev(kw, dtype)), eps=eps, temp_coef=float(qt.get("coef", 0.0)),
+                  temp_every=int(qt.get("every", 0)), values_are_keys=int(left))
+    ex = AttnExtra(window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)), max_kv_len=max_kv)
+
+    def step(rows_of):  # rows_of[r] = (first position, one past the last)
+        x = torch.cat([qkv[r][a:b] for r, (a, b) in enumerate(rows_of)])
+        p = [q for a, b in rows_of for q in range(a, b)]
+        rq = [r for r, (a, b) in enumerate(rows_of) for _ in range(a, b)]
+        T = len(p)
+        if T == 0:
+            return None
+        qo, out = torch.zeros(T, H * D, dtype=dtype, device="cuda"), torch.zeros(T, H * Dv, dtype=dtype, device="cuda")
+        a = (P(i32(p)), P(i32(rq)), P(i32(off)), P(i32(pages)))
+        assert lib.pk_gqa_norm_append(P(dev(x, dtype)), n_all, *a, qo.data_ptr(), cache.data_ptr(), stride, ps, H, G, D, Dv, rot["dims"] if rot else 0, 0,
+                                      freq.data_ptr() if rot else None, 1.0, C.byref(prep), T, f32, None) == 0
+        assert lib.pk_gqa_attention_ex(qo.data_ptr(), cache.data_ptr(), P(dev(sink, dtype)), *a, out.data_ptr(), stride, ps, T, H, G, D, Dv,
+                                       float(mx["scale"]), 0, C.byref(ex), f32, None) == 0
+        torch.cuda.synchronize()
+        return out.float().cpu()
+
+    step([(0, s) for s in starts])
+    return step([(s, n) for s, n in zip(starts, lens)])
+
+
+def oracle_attention(mx, kind, qkv, qw, kw, sink, lo, hi, eps=1e-5):
+    """The oracle's attention with identity projections: its input `h` IS the stacked projection output."""
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    nq, nk = H * D, G * D
+    nv = 0 if kind == "left" else G * Dv
+    eye = torch.eye(nq + nk + nv, dtype=F64)
+    w = {"q": eye[:nq], "k": eye[nq:nq + nk], "v": eye[nq + nk:], "q.norm": qw, "k.norm": kw, "sink": sink, "o": torch.eye(H * Dv, dtype=F64)}
+    w = {k: v.to(F64) for k, v in w.items()}
+    f = O.keys_as_values_attention if kind == "left" else O.windowed_attention
+    return f(qkv[:hi].to(F64), w, "", mx, torch.arange(hi), eps)[lo:].to(F32)
+
+
+# (kind, heads, kv heads, dim, vdim, window, kept first, rotated entries): bf16 with dim == vdim in {32, 64, 96, 128} runs on the tensor cores
+ATTN_SHAPES = [("attention", 3, 1, 20, 12, 50, 7, 8), ("attention", 6, 2, 32, 32, 48, 20, 32), ("attention", 4, 4, 64, 64, 100, 70, 16),
+               ("attention", 2, 1, 128, 128, 64, 3, 128), ("attention", 5, 5, 40, 72, 33, 0, 40), ("attention", 2, 1, 96, 96, 30, 130, 0),
+               ("attention", 4, 2, 32, 32, 0, 0, 16), ("left", 6, 2, 32, 32, 0, 0, 0), ("left", 3, 3, 24, 24, 0, 0, 0), ("left", 2, 1, 128, 128, 0, 0, 0)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("kind,H,G,D,Dv,size,keep,dims", ATTN_SHAPES)
+def test_attention_ragged_batch(lib, dtype, kind, H, G, D, Dv, size, keep, dims):
+    """three requests in one launch: a 70-token portion that starts at position 90 and lets the window leave the kept tokens behind,
+    one decoded token at position 199, and the first 5 tokens of a sequence"""
+    if kind == "left":
+        mx = par(H, G, D, 1, 8, 8, 1, 2, 1, coef=0.6, every=32)["mixer"]["left"]
+    else:
+        mx = att(H, G, D, Dv, size, keep, rot_dims=dims)["mixer"]
+    g = torch.Generator().manual_seed(3)
+    lens, starts = [160, 200, 5], [90, 199, 0]
+    n_all = H * D + G * D + (0 if kind == "left" else G * Dv)
+    qkv = [torch.randn(n, n_all, generator=g).to(dtype).to(F32) for n in lens]
+    nw = (D, D) if kind == "left" else (H * D, G * D)
+    qw, kw = [(1 + 0.3 * torch.randn(n, generator=g)).to(dtype).to(F32) for n in nw]
+    sink = (1.5 * torch.randn(H, generator=g)).to(dtype).to(F32)
+    mx["scale"] = 2.0 / math.sqrt(D)
+    got = run_attention(lib, dtype, mx, kind, qkv, qw, kw, sink, starts, lens)
+    want = torch.cat([oracle_attention(mx, kind, qkv[r], qw, kw, sink, starts[r], lens[r]) for r in range(3)])
+    tol = 3e-5 if dtype == F32 else 4e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("D", [32, 24])
+def test_decoded_tokens_of_unequal_contexts_in_one_launch(lib, dtype, D):
+    """contexts of 1500, 130 and 2 positions; bf16 with head size 32 splits the key axis over CTAs (with and without a known longest context)"""
+    mx = att(4, 2, D, D, 600, 40, rot_dims=8)["mixer"]
+    g = torch.Generator().manual_seed(6)
+    lens = [1500, 130, 2]
+    starts = [n - 1 for n in lens]
+    n_all = 4 * D + 2 * D + 2 * D
+    qkv = [torch.randn(n, n_all, generator=g).to(dtype).to(F32) for n in lens]
+    qw, kw = (1 + 0.3 * torch.randn(4 * D, generator=g)).to(dtype).to(F32), (1 + 0.3 * torch.randn(2 * D, generator=g)).to(dtype).to(F32)
+    sink = torch.zeros(4)
+    want = torch.cat([oracle_attention(mx, "attention", qkv[r], qw, kw, sink, starts[r], lens[r]) for r in range(3)])
+    for max_kv in (0, 1500):
+        got = run_attention(lib, dtype, mx, "attention", qkv, qw, kw, sink, starts, lens, max_kv=max_kv)
+        tol = 3e-5 if dtype == F32 else 4e-2
+        assert torch.allclose(got, want, atol=tol, rtol=tol), max_kv
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("prompt", [False, True])
+@pytest.mark.parametrize("D,size,keep", [(32, 300, 20), (24, 64, 5), (32, 5, 70), (64, 130, 64)])
+def test_single_keys_stand_out_at_the_window_and_the_kept_tokens(lib, dtype, prompt, D, size, keep):
+    """One key is aimed at with a steep score, so the output must be that key's value: the oldest position the window still holds, a
+    kept first token far back, on both sides of page borders, the query's own position.  The position just behind the window, the
+    first position that is no longer kept, or one past the query is hidden: the output must then NOT be that key's value (and equal the
+    oracle's, as in every case).  `prompt`: the queries sit in a 40-token portion (bf16 with head size 32 / 64: tensor-core kernel),
+    else they are decoded tokens."""
+    H = 2
+    mx = att(H, 1, D, D, size, keep, rot_dims=0, scale=30.0 / D)["mixer"]
+    n = 700
+    g = torch.Generator().manual_seed(4)
+    val = torch.randn(n, D, generator=g).to(dtype).to(F32)
+    key = torch.nn.functional.normalize(torch.randn(n, D, generator=g), dim=-1)
+    sink, ones_q, ones_k = torch.full((H,), 12.0), torch.ones(H * D), torch.ones(D)
+    qp = 690
+    cases = [(qp, qp - size + 1, True), (qp, qp - size, qp - size < keep), (qp, keep - 1, True), (qp, keep, keep > qp - size), (qp, 0, True), (qp, qp, True),
+             (qp, qp + 1, False), (qp, 15 if keep > 15 else qp - min(15, size - 1), True), (qp, 16 if keep > 16 else qp - min(16, size - 1), True), (qp, qp - size // 2, True),
+             (size + keep + 3, keep, False), (size + keep + 3, keep - 1, True), (keep + 1, keep, True), (max(size - 1, 1), 0, True)]
+    for q_at, kp, visible in cases:
+        if kp < 0 or kp >= n:
+            continue
+        qkv = torch.zeros(n, H * D + 2 * D)
+        qkv[:, H * D:H * D + D], qkv[:, H * D + D:] = key, val
+        qkv[q_at, :D] = key[kp]  # head 0 aims at position kp; head 1 asks nothing (uniform scores)
+        qkv = qkv.to(dtype).to(F32)
+        hi = max(q_at, kp) + 1
+        start = max(q_at - 39, 0) if prompt else q_at
+        got = run_attention(lib, dtype, mx, "attention", [qkv], ones_q, ones_k, sink, [start], [hi], eps=1e-6)[q_at - start]
+        want = oracle_attention(mx, "attention", qkv, ones_q, ones_k, sink, q_at, hi, eps=1e-6)[0]
+        assert torch.allclose(got, want, atol=1e-4 if dtype == F32 else 6e-2), (q_at, kp)
+        if visible:
+            assert torch.allclose(got[:D], val[kp], atol=3e-2 if dtype == F32 else 8e-2), (q_at, kp)
+        else:
+            assert (got[:D] - val[kp]).norm() > 0.5 * val[kp].norm(), (q_at, kp)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_sink_query_factor_and_key_values_on_two_keys(lib, dtype):
+    """two cached positions, one head: the weights are exp(s_j) / (exp(s_0) + exp(s_1) + exp(sink)) with s = q.k * scale * factor(p); the
+    values are the keys BEFORE their norm"""
+    D = 16
+    mx = par(1, 1, D, 1, 8, 8, 1, 2, 1, coef=0.9, every=1, scale=0.3)["mixer"]["left"]
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(2, 2 * D, generator=g).to(dtype).to(F32)
+    qkv[:, D:] *= torch.tensor([[3.0], [0.2]])  # keys of very different length: their norm must not reach the values
+    qw, kw, sink = torch.ones(D), torch.ones(D), torch.tensor([0.4])
+    got = run_attention(lib, dtype, mx, "left", [qkv], qw, kw, sink, [1], [2], eps=1e-6)[0]
+    q, k = O.rms(qkv[1, :D], 1e-6) * (1 + 0.9 * math.log(2 + 1)), O.rms(qkv[:, D:], 1e-6)
+    s = (k @ q) * 0.3
+    wts = torch.exp(s) / (torch.exp(s).sum() + math.exp(0.4))
+    want = wts @ qkv[:, D:]
+    assert torch.allclose(got, want, atol=1e-5 if dtype == F32 else 3e-2)
+    assert wts.sum() < 0.999  # the sink takes its share
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("taps", [1, 2, 4])
+def test_convolution_with_bias_carries_its_tail_through_portions(lib, dtype, taps):
+    """two requests, fed in portions of 1, 2, 3 and 7 tokens in turn (shorter and longer than the tail), slots swapped"""
+    P = Hold()
+    Cn, ld = 20, 27
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(30, Cn, generator=g).to(dtype).to(F32), torch.randn(22, Cn, generator=g).to(dtype).to(F32)]
+    cw, cb = (0.7 * torch.randn(Cn, taps, generator=g)).to(dtype).to(F32), (0.5 * torch.randn(Cn, generator=g)).to(dtype).to(F32)
+    want = []
+    for x in xs:
+        y = O.causal_conv(x, cw, cb)
+        want.append(y * torch.sigmoid(y))
+    slot_stride = 5 + max(taps - 1, 0) * Cn
+    state = torch.zeros(3, slot_stride, device="cuda")
+    slots, at, got = [2, 0], [0, 0], [[], []]
+    sizes, k = [1, 2, 3, 7], 0
+    while any(at[r] < len(xs[r]) for r in range(2)):
+        live = [r for r in range(2) if at[r] < len(xs[r])]
+        ns = [min(sizes[(k + r) % 4], len(xs[r]) - at[r]) for r in live]
+        rows = torch.zeros(sum(ns), ld)
+        rows[:, 3:3 + Cn] = torch.cat([xs[r][at[r]:at[r] + n] for r, n in zip(live, ns)])
+        req = [e for e, n in enumerate(ns) for _ in range(n)]
+        row0 = [sum(ns[:e]) for e in range(len(ns))]
+        out = torch.zeros(sum(ns), Cn, dtype=dtype, device="cuda")
+        x_d = dev(rows, dtype)
+        assert lib.pk_causal_conv_silu_bias(x_d.data_ptr() + 3 * x_d.element_size(), ld, P(dev(cw, dtype)), P(dev(cb, dtype)), state.data_ptr() + 5 * 4,
+                                            slot_stride, P(i32(req)), P(i32([slots[r] for r in live])), P(i32(row0)), P(i32(ns)), out.data_ptr(), Cn, Cn,
+                                            taps, sum(ns), len(ns), int(dtype == F32), None) == 0
+        torch.cuda.synchronize()
+        o = out.float().cpu()
+        for e, (r, n) in enumerate(zip(live, ns)):
+            got[r].append(o[row0[e]:row0[e] + n])
+            at[r] += n
+        k += 1
+    for r in range(2):
+        assert torch.allclose(torch.cat(got[r]), want[r], atol=1e-5 if dtype == F32 else 3e-2), r
+
+
+def plain_state_space(x, B, Cm, dt_raw, a_log, dt_bias, d_skip, S):
+    """token by token in fp64: x [T, H, P], B / Cm [T, G, N], dt_raw [T, H]; S [H, N, P] is updated in place"""
+    T, H, _ = x.shape
+    G = B.shape[1]
+    y = torch.zeros_like(x)
+    for t in range(T):
+        for h in range(H):
+            g = h // (H // G)
+            step = torch.nn.functional.softplus(dt_raw[t, h] + dt_bias[h], threshold=1e9)
+            S[h] = torch.exp(-torch.exp(a_log[h]) * step) * S[h] + step * torch.outer(B[t, g], x[t, h])
+            y[t, h] = S[h].T @ Cm[t, g] + d_skip[h] * x[t, h]
+    return y
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,N,Pv", [(3, 1, 20, 24), (4, 2, 32, 48), (2, 2, 128, 64), (1, 1, 6, 150), (6, 3, 200, 8)])
+def test_state_space_recurrence_in_portions_over_reused_slots(lib, dtype, H, G, N, Pv):
+    """two sequences advance in portions of 1, 37 and 2 tokens through slots 2 and 0; the state is carried in the slot"""
+    P = Hold()
+    g = torch.Generator().manual_seed(9)
+    lens = [45, 60]
+    Cn = H * Pv + 2 * G * N
+    ld, ld_dt, dt_off = Cn + 8, H + 3, 2
+    xbc = [torch.randn(n, Cn, generator=g).to(dtype).to(F32) for n in lens]
+    dts = [torch.randn(n, H, generator=g).to(dtype).to(F32) for n in lens]
+    a_log, dt_bias, d_skip = 0.5 * torch.randn(H, generator=g) - 1.0, 0.5 * torch.randn(H, generator=g), 1 + 0.3 * torch.randn(H, generator=g)
+    want = []
+    for x, d in zip(xbc, dts):
+        S = torch.zeros(H, N, Pv, dtype=F64)
+        x64 = x.to(F64)
+        want.append(plain_state_space(x64[:, :H * Pv].reshape(-1, H, Pv), x64[:, H * Pv:H * Pv + G * N].reshape(-1, G, N), x64[:, H * Pv + G * N:].reshape(-1, G, N),
+                                      d.to(F64), a_log.to(F64), dt_bias.to(F64), d_skip.to(F64), S).reshape(-1, H * Pv).to(F32))
+    slot_stride = H * N * Pv + 11
+    state = torch.zeros(3, slot_stride, device="cuda")
+    slots, at, got = [2, 0], [0, 0], [[], []]
+    sizes, k = [1, 37, 2], 0
+    while any(at[r] < lens[r] for r in range(2)):
+        live = [r for r in range(2) if at[r] < lens[r]]
+        ns = [min(sizes[(k + r) % 3], lens[r] - at[r]) for r in live]
+        T = sum(ns)
+        rows, drows = torch.zeros(T, ld), torch.zeros(T, ld_dt)
+        rows[:, 8:] = torch.cat([xbc[r][at[r]:at[r] + n] for r, n in zip(live, ns)])
+        drows[:, dt_off:dt_off + H] = torch.cat([dts[r][at[r]:at[r] + n] for r, n in zip(live, ns)])
+        row0 = [sum(ns[:e]) for e in range(len(ns))]
+        out = torch.zeros(T, H * Pv, device="cuda")
+        assert lib.pk_ssd_seq(P(dev(rows, dtype)), ld, 8, 8 + H * Pv, 8 + H * Pv + G * N, P(dev(drows, dtype)), ld_dt, dt_off, P(a_log.cuda()), P(dt_bias.cuda()),
+                              P(d_skip.cuda()), state.data_ptr(), slot_stride, P(i32([slots[r] for r in live])), P(i32(row0)), P(i32(ns)), out.data_ptr(),
+                              H, G, N, Pv, len(ns), int(dtype == F32), None) == 0
+        torch.cuda.synchronize()
+        o = out.cpu()
+        for e, (r, n) in enumerate(zip(live, ns)):
+            got[r].append(o[row0[e]:row0[e] + n])
+            at[r] += n
+        k += 1
+    for r in range(2):
+        assert torch.allclose(torch.cat(got[r]), want[r], atol=2e-4, rtol=2e-4), r
+    assert state[1].abs().max().item() == 0.0  # the slot nobody owned is untouched
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("groups", [1, 3, 6])
+def test_gate_before_the_grouped_norm(lib, dtype, groups):
+    P = Hold()
+    T, inner, ld, off, eps = 5, 6 * 14, 6 * 14 + 9, 4, 1e-5
+    g = torch.Generator().manual_seed(10)
+    y, z = 3 * torch.randn(T, inner, generator=g), torch.zeros(T, ld)
+    z[:, off:off + inner] = torch.randn(T, inner, generator=g)
+    z = z.to(dtype).to(F32)
+    wn = (1 + 0.3 * torch.randn(inner, generator=g)).to(dtype).to(F32)
+    out = torch.zeros(T, inner, dtype=dtype, device="cuda")
+    assert lib.pk_head_norm_gate(P(y.cuda()), None, P(dev(wn, dtype)), inner // groups, P(dev(z, dtype)), ld, off, out.data_ptr(), T, groups, inner // groups,
+                                 eps, 2, int(dtype == F32), None) == 0
+    torch.cuda.synchronize()
+    zz = z[:, off:off + inner]
+    gated = y * (zz * torch.sigmoid(zz))
+    want = O.rms(gated.reshape(T, groups, -1), eps).reshape(T, inner) * wn
+    assert torch.allclose(out.float().cpu(), want, atol=1e-5 if dtype == F32 else 3e-2)
+
+
+def test_router_takes_the_largest_logits_and_weighs_them_alone(lib):
+    P = Hold()
+    T, E, top, ld = 9, 11, 3, 14
+    g = torch.Generator().manual_seed(11)
+    z, b = 2 * torch.randn(T, ld, generator=g), torch.randn(E, generator=g)
+    z[0, :E] = -50.0 - torch.arange(E)  # all far below zero: the weights still sum to one
+    ids, wts = torch.zeros(T, top, dtype=torch.int32, device="cuda"), torch.zeros(T, top, device="cuda")
+    assert lib.pk_router_topk_logits(P(z.cuda()), ld, P(b.cuda()), ids.data_ptr(), wts.data_ptr(), T, E, top, 1.0, None) == 0
+    torch.cuda.synchronize()
+    val, idx = torch.topk(z[:, :E] + b, top, -1)
+    assert (ids.cpu().long() == idx).all()
+    assert torch.allclose(wts.cpu(), torch.softmax(val, -1), atol=1e-6)
+    assert torch.allclose(wts.cpu().sum(-1), torch.ones(T), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("T", [3, 70])
+def test_clamped_experts_per_token_and_bucketed(lib, dtype, T):
+    """T = 70 in bf16 runs bucketed by expert on the tensor cores; pre-activations are scaled so that every clamp bites"""
+    if dtype == F32 and T == 70:
+        pytest.skip("the bucketed form is bf16 only")
+    P = Hold()
+    W, E, top, ff, sff, limit, slimit = 48, 6, 2, 24, 16, 0.7, 1.1
+    g = torch.Generator().manual_seed(12)
+    rnd = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    h = rnd(T, W).to(dtype).to(F32)
+    w = {"router": rnd(E, W), "router.b": rnd(E)}
+    for e in range(E):
+        w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = 2 * rnd(ff, W) / 7, 2 * rnd(ff, W) / 7, rnd(W, ff) / 5
+    w["shared.gate"], w["shared.up"], w["shared.down"] = 2 * rnd(sff, W) / 7, 2 * rnd(sff, W) / 7, rnd(W, sff) / 4
+    w = {k: v.to(dtype).to(F32) for k, v in w.items()}
+    mlp = moe(E, top, ff, limit, sff, slimit)
+    want = O.expert_mixture(h, w, "", mlp)
+    idx, wt = O.route(h, w, "", top)
+    up = torch.stack([torch.stack([w[f"e{e}.gate"], w[f"e{e}.up"]], 1).reshape(2 * ff, W) for e in range(E)])  # gate / up rows interleaved
+    down = torch.stack([w[f"e{e}.down"] for e in range(E)])
+    f32 = int(dtype == F32)
+    gu = torch.cat([h @ w["shared.gate"].T, h @ w["shared.up"].T], 1).to(dtype)
+    act = torch.zeros(T, sff, dtype=dtype, device="cuda")
+    assert lib.pk_act_clamped(P(gu.cuda()), act.data_ptr(), sff, T, slimit, O.GATE_SLOPE, f32, None) == 0
+    torch.cuda.synchronize()
+    shared = (act.float().cpu() @ w["shared.down"].T).to(dtype)
+    y = torch.zeros(T, W, device="cuda")
+    ids_d, wt_d, x_d = idx.to(torch.int32).cuda(), wt.float().cuda(), dev(h, dtype)
+    if T >= 32 and dtype == BF16:
+        ws = torch.zeros(lib.pk_moe_grouped_workspace_bytes(T, top, E, W, ff) + 256, dtype=torch.uint8, device="cuda")
+        base = (ws.data_ptr() + 255) // 256 * 256
+        assert lib.pk_moe_grouped_act_p(x_d.data_ptr(), P(dev(up, dtype)), P(dev(down, dtype)), ids_d.data_ptr(), wt_d.data_ptr(), P(shared.cuda()), None,
+                                        y.data_ptr(), base, T, top, E, W, ff, 2, limit, O.GATE_SLOPE, None) == 0
+    else:
+        hid = torch.zeros(T, top, ff, dtype=dtype, device="cuda")
+        assert lib.pk_moe_up_act_p(x_d.data_ptr(), P(dev(up, dtype)), ids_d.data_ptr(), hid.data_ptr(), T, top, W, ff, 2, limit, O.GATE_SLOPE, f32, None) == 0
+        assert lib.pk_moe_down_combine(hid.data_ptr(), P(dev(down, dtype)), ids_d.data_ptr(), wt_d.data_ptr(), P(shared.cuda()), None, y.data_ptr(), T, top,
+                                       W, ff, f32, None) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(y.cpu(), want, atol=2e-5 if dtype == F32 else 5e-2, rtol=2e-5 if dtype == F32 else 5e-2)
+    g_pre = h @ w["e0.gate"].T
+    assert (g_pre > limit).any() and (g_pre.abs() < limit).any()  # both sides of the clamp occur
+
+
+# ------------------------------------------------------------------ one-layer models: each branch alone
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("silent", ["left", "right"])
+def test_each_branch_of_the_parallel_mixer_alone(dtype, silent):
+    """the silenced branch's norm weight is zero, so the layer's result is half the other branch's normed output"""
+    cfg = model_cfg([(par(4, 2, 16, 3, 20, 12, 1, 3, 3, every=8), None)], vocab=64, width=48)
+    w = make_weights(cfg, 14, SHARP[dtype])
+    w[f"l0.mix.{silent}.out"] = torch.zeros_like(w[f"l0.mix.{silent}.out"])
+    toks = tokens_for(cfg, 90, 3)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    got = torch.cat([m.step([(rid, toks[:50])], [list(range(50))])] + [m.step([(rid, [t])]) for t in toks[50:]])
+    assert close(got, oracle_logits(cfg, w, toks), dtype)
+    m.close()
+
+
+# ------------------------------------------------------------------ the model through its own entry points
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_prompt_with_residual_after_every_layer(name, dtype):
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 21, SHARP[dtype])
+    toks = tokens_for(cfg, 150, 2)
+    m = build(cfg, w, dtype)
+    m.keep_trail(True)
+    rid = m.alloc_request()
+    got = m.step([(rid, toks)], [list(range(len(toks)))])
+    trail = []
+    want = oracle_logits(cfg, w, toks, trail)
+    tr = m.trail(len(toks))
+    assert len(trail) == len(cfg["layers"])
+    for i, x in enumerate(trail):
+        e = (tr[i] - x.to(F32)).abs().amax(-1) / x.abs().max()  # per token; in bf16 a routing decision that rounding flips moves single tokens
+        assert (e.max() < 1e-4) if dtype == F32 else (e.quantile(0.9) < 0.1), (i, e.max())
+    assert close(got, want, dtype)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_prefill_against_token_by_token_decoding(name, dtype):
+    """the first tokens as one prompt, the rest one by one through the cache and the state slots (every window's edge and the kept
+    tokens are passed while decoding); then the same sequence decoded from its very first token"""
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 22, SHARP[dtype])
+    toks = tokens_for(cfg, 130, 3)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    for first in (60, 1):
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:first])], [list(range(first))])]
+        for t in range(first, len(toks)):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert close(torch.cat(rows), want, dtype), first
+        m.drop_request(rid)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("sizes", [(2,), (3, 2, 16, 1, 37, 5), (64, 2, 2), (33, 1)])
+def test_prompt_in_portions(dtype, sizes):
+    """portions cut anywhere (inside pages, windows and the convolution's tail), down to two tokens"""
+    cfg = cfg_general()
+    w = make_weights(cfg, 23, SHARP[dtype])
+    toks = tokens_for(cfg, 140, 4)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    rows, at, k = [], 0, 0
+    while at < len(toks):
+        n = min(sizes[k % len(sizes)], len(toks) - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at, k = at + n, k + 1
+    assert close(torch.cat(rows), want, dtype)
+    m.close()
+
+
+def random_cfg(seed):
+    """layer order, every size and every constant drawn at random (seeded); some layers borrow an earlier or a later layer's weights"""
+    r = random.Random(seed)
+    layers = []
+    for _ in range(r.randint(2, 4)):
+        heads = r.choice([1, 2, 3, 4, 6])
+        kv = r.choice([d for d in (1, 2, 3, 4, 6) if heads % d == 0])
+        if r.random() < 0.5:
+            dim = r.choice([8, 12, 20, 32, 40, 64])
+            vdim = dim if r.random() < 0.5 else r.choice([8, 16, 28, 48])
+            size = r.choice([0, r.randint(1, 70)])
+            l = att(heads, kv, dim, vdim, size, r.choice([0, r.randint(1, 40)]) if size else 0, rot_dims=r.choice([0, 2, dim // 2 // 2 * 2, dim]),
+                    scaling=r.random() < 0.6, base=r.choice([100.0, 10000.0, 500000.0]), scale=r.uniform(0.05, 0.4))
+        else:
+            sh = r.choice([1, 2, 3, 4, 6])
+            sg = r.choice([d for d in (1, 2, 3) if sh % d == 0])
+            sv = r.choice([4, 8, 20, 36])
+            ng = r.choice([d for d in (1, 2, 3, 4, 6) if (sh * sv) % d == 0])
+            l = par(heads, kv, r.choice([8, 12, 32, 40, 96]), sh, sv, r.choice([4, 16, 24, 64, 100]), sg, r.randint(1, 5), ng, coef=r.uniform(0.1, 1.0),
+                    every=r.choice([1, 5, 32, 1000]), scale=r.uniform(0.05, 0.4))
+        mlp = None
+        if r.random() < 0.8:
+            experts = r.randint(1, 9)
+            sff = r.choice([0, 8, 20])
+            mlp = moe(experts, r.randint(1, experts), r.choice([8, 20, 32, 44]), r.uniform(0.5, 3.0), sff, r.uniform(0.5, 3.0) if sff else 0.0)
+        layers.append((l, mlp))
+    n_own = len(layers)
+    for _ in range(r.randint(0, 2)):
+        layers.insert(r.randint(0, len(layers)), -1)
+    own_at = [i for i, l in enumerate(layers) if l != -1]
+    layers = [l if l != -1 else own_at[r.randrange(n_own)] for l in layers]
+    return model_cfg(layers, vocab=r.randint(40, 300), width=r.choice([24, 36, 40, 64, 100]), eps=r.choice([1e-5, 1e-6]), embed=r.uniform(0.5, 4.0),
+                     logit=r.uniform(0.2, 2.0), cap=r.choice([0.0, 5.0, 30.0]))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("seed", range(14))
+def test_configurations_drawn_at_random(seed, dtype):
+    """a prompt in portions of random sizes (some >= 32 tokens, so that the tensor-core and bucketed kernels run where the sizes
+    allow), then decoded tokens, against the oracle over the whole sequence"""
+    cfg = random_cfg(100 + seed)
+    w = make_weights(cfg, 200 + seed, SHARP[dtype])
+    toks = tokens_for(cfg, 120, seed)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    r = random.Random(seed)
+    rows, at = [], 0
+    while at < len(toks):
+        n = 1 if at >= 100 else min(r.choice([1, 2, 5, 17, 33, 48]), 100 - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at += n
+    assert close(torch.cat(rows), want, dtype), cfg
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_unequal_batches_reuse_pages_and_slots(dtype):
+    """Seven unequal requests through three request slots and a pool of 18 pages: portions of some beside single tokens of others in
+    every step; finished requests hand their pages and state slot to the next one.  Every request must come out as when it runs alone."""
+    from pegainfer_b200.engine import Engine
+    cfg = cfg_general()
+    w = make_weights(cfg, 24, SHARP[dtype])
+    lens = [70, 9, 40, 101, 1, 33, 64]
+    prompts = [tokens_for(cfg, n, 30 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, p) for p in prompts]
+    m = build(cfg, w, dtype, max_tokens=18 * 16, max_requests=3)
+    eng = Engine(m)
+    got = [[] for _ in prompts]
+    at = [0] * len(prompts)
+    waiting, live, step, seen_pages = list(range(len(prompts))), [], 0, set()
+    portion = [5, 1, 17, 2, 1, 30, 3]
+    pages_of = lambda i: (lens[i] + 15) // 16  # noqa: E731
+    while waiting or live:
+        while waiting and len(live) < 3 and sum(pages_of(i) for i in live) + pages_of(waiting[0]) <= 18:
+            live.append(waiting.pop(0))
+        entries = []
+        for i in live:
+            n = min(portion[(step + i) % len(portion)], lens[i] - at[i])
+            entries.append((f"q{i}", prompts[i][at[i]:at[i] + n], list(range(n))))
+        out = eng.step(entries, [])
+        r = 0
+        for (name, t, _), i in zip(entries, list(live)):
+            got[i].append(out[r:r + len(t)])
+            r += len(t)
+            at[i] += len(t)
+            seen_pages.update(m.request_pages(eng.slots[name]))
+            if at[i] == lens[i]:
+                eng.release(name)
+                live.remove(i)
+        step += 1
+    assert sum((n + 15) // 16 for n in lens) > 18 >= len(seen_pages)  # pages were handed out again
+    for i in range(len(prompts)):
+        assert close(torch.cat(got[i]), want[i], dtype), i
+    m.close()
+
+
+def test_rejected_step_leaves_lengths_pages_and_state_untouched():
+    cfg = cfg_general()
+    w = make_weights(cfg, 25)
+    toks = tokens_for(cfg, 60, 5)
+    m = build(cfg, w, F32, max_tokens=64, max_requests=2)
+    a, b = m.alloc_request(), m.alloc_request()
+    m.step([(a, toks[:20])])
+    free = m.available_pages()
+    with pytest.raises(RuntimeError):
+        m.step([(a, toks[20:25]), (b, toks[:60])])  # b does not fit: nothing of the step may stay
+    assert m.seq_len(a) == 20 and m.seq_len(b) == 0 and m.available_pages() == free
+    got = m.step([(a, toks[20:40])], [list(range(20))])
+    assert close(got, oracle_logits(cfg, w, toks[:40])[20:], F32)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_long_decoding_and_captured_steps(dtype):
+    """a 300-token prompt and 260 decoded tokens (captured launch sequences from the second step of a kind on, across a graph bucket
+    border at 512, with a window that leaves the prompt behind while the kept tokens stay) against the same steps run eagerly and
+    against the oracle"""
+    cfg = model_cfg([(att(4, 2, 32, 32, 128, 24, rot_dims=16), moe(8, 2, 32, 1.0, 32, 1.5)), (par(4, 1, 32, 2, 32, 32, 1, 4, 2, every=64), None), 0, 1],
+                    vocab=96, width=64)
+    w = make_weights(cfg, 26, SHARP[dtype])
+    toks = tokens_for(cfg, 560, 6)
+    outs = []
+    for graph in (True, False):
+        m = build(cfg, w, dtype, max_tokens=1024)
+        m.use_graph(graph)
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:300])])]
+        for t in range(300, 560):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert (m.graph_count() > 0) == graph
+        outs.append(torch.cat(rows))
+        m.close()
+    assert torch.allclose(outs[0], outs[1], atol=1e-5 if dtype == F32 else 2e-2)
+    want = oracle_logits(cfg, w, toks)[299:]
+    assert close(outs[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_batched_decode_steps_of_unequal_requests(dtype):
+    """three prompts of unequal length admitted in one step, then 40 steps that carry one token of each (replayed as a captured
+    launch sequence from the third step on); every request must come out as when it runs alone"""
+    cfg = cfg_general()
+    w = make_weights(cfg, 29, SHARP[dtype])
+    lens = [23, 61, 4]
+    seqs = [tokens_for(cfg, n + 40, 50 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, q) for q in seqs]
+    m = build(cfg, w, dtype)
+    rids = [m.alloc_request() for _ in lens]
+    got = [[] for _ in lens]
+    out = m.step([(r, q[:n]) for r, q, n in zip(rids, seqs, lens)])
+    for i in range(3):
+        got[i].append(out[i:i + 1])
+    for t in range(40):
+        out = m.step([(r, [q[n + t]]) for r, q, n in zip(rids, seqs, lens)])
+        for i in range(3):
+            got[i].append(out[i:i + 1])
+    assert m.graph_count() > 0
+    for i, n in enumerate(lens):
+        assert close(torch.cat(got[i]), want[i][n - 1:], dtype), i
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_greedy_generation_through_the_scheduler(dtype):
+    """the framework's own entry points: generate() of the model and the continuous-batching scheduler; teacher-forced check of
+    every generated token against the oracle's logits for the sequence the framework produced"""
+    from pegainfer_b200.engine import Engine
+    cfg = cfg_general()
+    w = make_weights(cfg, 27)
+    prompts = [tokens_for(cfg, n, 40 + n) for n in (5, 37, 1, 64, 18)]
+    m = build(cfg, w, dtype, max_tokens=512, max_requests=3)
+    outs = Engine(m).generate(prompts, 12, max_live=3, token_budget=48)
+    alone, _, _ = m.generate(prompts[1], 12)
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        lg = oracle_logits(cfg, w, p + o[:-1])[len(p) - 1:].to(F32)
+        top2 = lg.topk(2, -1).values
+        gap_ok = (top2[:, 0] - top2[:, 1]) < (1e-3 if dtype == F32 else 0.15) * lg.std()
+        assert ((lg.argmax(-1) == torch.tensor(o)) | gap_ok).all()
+    if dtype == F32:
+        assert alone == outs[1]
+    m.close()
+
+
+def test_checkpoint_folder_through_the_registry_and_the_trace_tool(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    from pegainfer_b200.registry import architecture_of, load_model
+    cfg = cfg_edges()
+    w = make_weights(cfg, 28)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    assert architecture_of(str(tmp_path)) == "Goguzen"
+    m = load_model(str(tmp_path), "float32", max_tokens=256)
+    toks = tokens_for(cfg, 40, 7)
+    rid = m.alloc_request()
+    want = oracle_logits(cfg, w, toks)
+    assert close(m.step([(rid, toks)], [list(range(40))]), want, F32)
+    m.close()
+    # the same through the trace tool in a process of its own: two portions of one request beside a second request
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:25], "want": [0, 24]}, {"id": "b", "tokens": toks[:3], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[25:], "want": [14]}, {"id": "b", "tokens": toks[3:9], "want": [5]}], "end": ["a", "b"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600,
+                       env={k: v for k, v in os.environ.items() if not k.startswith("OMP_")} | {"PYTHONPATH": root})
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.split("\n") if l.startswith("done")] == ["done 0", "done 1"]
+    a0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1).copy())
+    a1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1).copy())
+    assert close(torch.cat([a0, a1]), want[[0, 24, 39, 8]], F32)
