@@ -807,6 +807,24 @@ def _nagosun_sizes():
     return {"w2048": nag(2048, 16, 8, 128, 6 * 1408 + 2816, (128, 64, 128, 512), 32768), "w1024": nag(1024, 8, 4, 128, 2 * 768 + 1536, (64, 32, 64, 256), 32768)}
 
 
+def _goguzen_sizes():
+    """Goguzen stacks of the same width, head count, expert count and vocabulary as the Risolorn stacks of `_risolorn_sizes` (its closest
+    relative on the same host: recurrent mixers beside sink attention, routed experts, fp32 residual): attention beside a state-space
+    branch, windowed attention, the first layer's weights once more, windowed attention; every layer with routed experts and a shared one.
+    The state-space branch is twice the model's width (heads of 64, state 128), as such layers usually are."""
+    def gog(width, heads, kv, dim, window, experts, top, eff, sff, vocab):
+        moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": sff, "limit": 7.0}}
+        att = {"type": "attention", "mlp": moe,
+               "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window, "keep_first": 64}, "scale": dim ** -0.5,
+                         "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}}
+        par = {"type": "parallel", "mlp": moe,
+               "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}},
+                         "right": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 8}}}
+        return {"architecture": "Goguzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+                "logit_softcap": 30.0, "layers": [par, att, dict(par, weights_of=0), att]}
+    return {"w2048": gog(2048, 16, 4, 128, 1024, 64, 6, 1408, 2816, 32768), "w1024": gog(1024, 8, 2, 64, 1024, 16, 2, 768, 1536, 32768)}
+
+
 def _measure_layered(vm, prompts, ctx, med, synthetic_prompt):
     """prefill tok/s per prompt length and decode tok/s at batch 1 and 4 of a model on the layer-list host"""
     res = {}
@@ -835,7 +853,7 @@ def _measure_layered(vm, prompts, ctx, med, synthetic_prompt):
 
 def run_arch_compare(args):
     """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  `--arch risolorn` /
-    `--arch nagosun`: that design's path beside both.  Wall clock around each public-API call (token ids from the host in, logits / token back out,
+    `--arch nagosun`: that design's path beside both.  `--arch goguzen`: that design's path beside Risolorn's and Qwen3's.  Wall clock around each public-API call (token ids from the host in, logits / token back out,
     stream synchronised), median of the repeats after warm-up; between repeats nothing else runs on the GPU.  One JSON line."""
     import torch
     from pegainfer_b200.model import ModelRuntimeConfig, Qwen3Model
@@ -843,7 +861,8 @@ def run_arch_compare(args):
     from pegainfer_b200.vamadra import VamadraConfig, VamadraModel, iter_random_weights as vam_weights
     reps, warm = max(3, min(args.steps, 20)), max(3, min(args.warmup, 5))
     prompts, ctx, dec_steps = [512, 2048], 2048, 32
-    out = {"metric": "prefill_and_decode_tok_s", "arch": args.arch, "beside": "qwen3" if args.arch == "vamadra" else "vamadra, qwen3", "dtype": "bf16",
+    beside = {"vamadra": "qwen3", "goguzen": "risolorn, qwen3"}.get(args.arch, "vamadra, qwen3")
+    out = {"metric": "prefill_and_decode_tok_s", "arch": args.arch, "beside": beside, "dtype": "bf16",
            "data": "synthetic", "n_gpus": 1,
            "timing": "wall clock around the public API call incl. host->device ids and device->host result, stream synchronised", "sizes": {}}
 
@@ -862,7 +881,13 @@ def run_arch_compare(args):
         if args.arch_size and name not in args.arch_size.split(","):
             continue
         row = {}
-        if args.arch == "risolorn":
+        if args.arch == "goguzen":
+            from pegainfer_b200.goguzen import GoguzenConfig, GoguzenModel, iter_random_weights as gog_weights
+            gcfg = GoguzenConfig.from_dict(_goguzen_sizes()[name])
+            gm = GoguzenModel(gcfg, gog_weights(gcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
+            row["goguzen"] = _measure_layered(gm, prompts, ctx, med, synthetic_prompt)
+            gm.close()
+        if args.arch in ("risolorn", "goguzen"):
             from pegainfer_b200.risolorn import RisolornConfig, RisolornModel, iter_random_weights as ris_weights
             rcfg = RisolornConfig.from_dict(_risolorn_sizes()[name])
             rm = RisolornModel(rcfg, ris_weights(rcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
@@ -874,10 +899,11 @@ def run_arch_compare(args):
             nm = NagosunModel(ncfg, nag_weights(ncfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
             row["nagosun"] = _measure_layered(nm, prompts, ctx, med, synthetic_prompt)
             nm.close()
-        vcfg = VamadraConfig.from_dict(vcfg_d)
-        vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
-        row["vamadra"] = _measure_layered(vm, prompts, ctx, med, synthetic_prompt)
-        vm.close()
+        if args.arch != "goguzen":
+            vcfg = VamadraConfig.from_dict(vcfg_d)
+            vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
+            row["vamadra"] = _measure_layered(vm, prompts, ctx, med, synthetic_prompt)
+            vm.close()
         qm = Qwen3Model(qcfg, iter_random_weights(qcfg, seed=0, device="cuda"),
                         ModelRuntimeConfig(enable_cuda_graph=True, fused=True, num_pages=(4 * (ctx + 64) + max(prompts)) // 16 + 8, max_batch=4))
         res = {}
@@ -920,7 +946,7 @@ def main():
     ap.add_argument("--weights", default="cpu", choices=["cpu", "cuda"],
                     help="cpu (default): the seed-0 CPU checkpoint the oracle fixtures were computed on; cuda: generated on "
                          "each GPU (fast; tuning sweeps only -- the parity key then reports a different checkpoint)")
-    ap.add_argument("--arch", default=None, choices=["vamadra", "risolorn", "nagosun"],
+    ap.add_argument("--arch", default=None, choices=["vamadra", "risolorn", "nagosun", "goguzen"],
                     help="instead of the headline workload: prefill / decode throughput of this design beside the closest existing ones at equal size")
     ap.add_argument("--arch-size", default=None, help="with --arch: comma-separated subset of the sizes (w2048,w1024)")
     args = ap.parse_args()

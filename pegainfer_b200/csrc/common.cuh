@@ -114,6 +114,9 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return r;
 }
 
+// ask for the cache line of `p` to be brought into L2 (no register, no wait): small weight vectors that a later phase of the kernel reads
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // ---- mbarrier + 1-D TMA bulk copy (cp.async.bulk) ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

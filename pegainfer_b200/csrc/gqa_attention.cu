@@ -91,19 +91,19 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
                                        float eps, float temp_coef, int temp_every, int v_from_k) {
   extern __shared__ float na_sm[];
   float* row = na_sm;             // [nq + nk]
-  float* inv = row + (H + G) * dim;  // [H + G] reciprocal root mean square per head
+  float* inv = row + (H + G) * dim;  // [H + G] sum of squares per head
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, p = pos[t], lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const E* src = qkv + (size_t)t * ld;
   const int nq = H * dim, nk = G * dim, nv = G * vdim, half = dims >> 1;
-  E* slot = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (nk + nv);
+  // the page lookup (three dependent loads) and the weights of the last phase travel while the row is loaded and summed
+  const int page = pages[page_off[req[t]] + p / page_size];
+  if (norm_kind)
+    for (int e = threadIdx.x * 64; e < (norm_kind == 1 ? dim : nq + nk); e += blockDim.x * 64)
+      prefetch_l2(norm_kind == 1 ? (e < dim ? qw + e : kw + e - dim) : (e < nq ? qw + e : kw + e - nq));  // a line of 64 entries each
+  if (norm_kind == 1 && threadIdx.x * 64 < dim) prefetch_l2(kw + threadIdx.x * 64);
   for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) row[e] = to_f(src[e]);
-  if (v_from_k) {
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) slot[nk + e] = src[nq + e];
-  } else {
-    for (int e = threadIdx.x; e < nv; e += blockDim.x) slot[nk + e] = src[nq + nk + e];
-  }
   __syncthreads();
   if (norm_kind) {
     for (int hd = warp; hd < H + G; hd += nw) {
@@ -113,29 +113,28 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
       if (lane == 0) inv[hd] = ss;
     }
     __syncthreads();
-    if (norm_kind == 1) {
-      if (threadIdx.x < H + G) inv[threadIdx.x] = 1.f / sqrtf(inv[threadIdx.x] / (float)dim + eps);
-      __syncthreads();
-    } else {
-      float sq = 0.f, sk = 0.f;
-      for (int hd = 0; hd < H; ++hd) sq += inv[hd];
-      for (int hd = 0; hd < G; ++hd) sk += inv[H + hd];
-      __syncthreads();
-      const float iq = 1.f / sqrtf(sq / (float)nq + eps), ik = 1.f / sqrtf(sk / (float)nk + eps);
-      for (int hd = threadIdx.x; hd < H + G; hd += blockDim.x) inv[hd] = hd < H ? iq : ik;
-      __syncthreads();
-    }
-    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
-      const bool is_q = e < nq;
-      const int el = is_q ? e : e - nq;
-      const E* w = is_q ? qw : kw;
-      row[e] *= inv[e / dim] * to_f(w[norm_kind == 1 ? el % dim : el]);
-    }
-    __syncthreads();
   }
+  // reciprocal root mean square of the whole q row / k row (norm_kind 2): the heads' sums added in head order by every thread
+  float iq = 1.f, ik = 1.f;
+  if (norm_kind == 2) {
+    float sq = 0.f, sk = 0.f;
+    for (int hd = 0; hd < H; ++hd) sq += inv[hd];
+    for (int hd = 0; hd < G; ++hd) sk += inv[H + hd];
+    iq = 1.f / sqrtf(sq / (float)nq + eps);
+    ik = 1.f / sqrtf(sk / (float)nk + eps);
+  }
+  // normed entry e of the row [q | k]
+  auto normed = [&](int e) {
+    if (!norm_kind) return row[e];
+    const bool is_q = e < nq;
+    const int el = is_q ? e : e - nq;
+    if (norm_kind == 1) return row[e] * (1.f / sqrtf(inv[e / dim] / (float)dim + eps)) * to_f((is_q ? qw : kw)[el % dim]);
+    return row[e] * (is_q ? iq : ik) * to_f((is_q ? qw : kw)[el]);
+  };
   const float stretch = temp_every > 0 ? 1.f + temp_coef * logf((float)((p + 1) / temp_every) + 1.f) : 1.f;
+  E* slot = cache + (size_t)page * page_stride + (size_t)(p % page_size) * (nk + nv);
   for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
-    float v = row[e];
+    float v = normed(e);
     const int d = e % dim;
     if (d < dims) {
       int i, pe;
@@ -151,10 +150,16 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
       }
       const float a = (float)p * freq[i];
       const float c = cosf(a) * mag, sn = sinf(a) * mag;
-      v = first ? v * c - row[pe] * sn : v * c + row[pe] * sn;
+      const float o = normed(pe);
+      v = first ? v * c - o * sn : v * c + o * sn;
     }
     if (e < nq) q_out[(size_t)t * nq + e] = from_f<E>(v * stretch);
     else slot[e - nq] = from_f<E>(v);
+  }
+  if (v_from_k) {
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) slot[nk + e] = src[nq + e];
+  } else {
+    for (int e = threadIdx.x; e < nv; e += blockDim.x) slot[nk + e] = src[nq + nk + e];
   }
 }
 

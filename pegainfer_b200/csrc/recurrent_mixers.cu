@@ -338,6 +338,41 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   }
 }
 
+// the same for few (token, head) pairs of many entries each (a decode step with wide norm groups): one CTA per pair
+template <typename E>
+__global__ void head_norm_gate_wide_kernel(const float* __restrict__ o, const float* __restrict__ den, const E* __restrict__ w, int w_stride,
+                                           const E* __restrict__ gate, int ld_gate, int gate_off, E* __restrict__ out, int H, int vdim, float eps,
+                                           int act) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const long pr = blockIdx.x, t = pr / H;
+  const int h = (int)(pr % H);
+  const float* orow = o + pr * vdim;
+  const float dn = den ? den[pr] : 1.f;
+  float v[4], ga[4];  // up to 4 entries per thread (vdim <= 4 * blockDim.x)
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int j = threadIdx.x + u * blockDim.x;
+    v[u] = 0.f;
+    ga[u] = 0.f;
+    if (j < vdim) {
+      const float gz = to_f(gate[(size_t)t * ld_gate + gate_off + h * vdim + j]);
+      ga[u] = act == 1 ? 1.f / (1.f + expf(-gz)) : gz / (1.f + expf(-gz));
+      v[u] = den ? orow[j] / dn : orow[j];
+      if (act == 2) v[u] *= ga[u];
+      ss = fmaf(v[u], v[u], ss);
+    }
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)vdim + eps);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int j = threadIdx.x + u * blockDim.x;
+    if (j < vdim) out[pr * vdim + j] = from_f<E>(act == 2 ? v[u] * inv * to_f(w[(size_t)h * w_stride + j]) : v[u] * inv * to_f(w[(size_t)h * w_stride + j]) * ga[u]);
+  }
+}
+
 template <typename E, int MODE>
 static int launch_seq(const SeqArgs& a, int entries, cudaStream_t st) {
   if (a.dim > 256) return -2;
@@ -410,6 +445,16 @@ extern "C" int pk_head_norm_gate(const float* o, const float* den, const void* w
                                  int tokens, int heads, int vdim, float eps, int act, int f32, pk_stream st) {
   if (!o || !w || !gate || !out || tokens <= 0 || heads <= 0 || vdim <= 0 || act < 0 || act > 2) return -1;
   const long pairs = (long)tokens * heads;
+  if (vdim >= 256 && vdim <= 4096 && pairs <= 1024) {  // few wide pairs: a CTA each, so that a decode step is not one warp's loop
+    const dim3 gw((unsigned)pairs), bw(vdim <= 512 ? 128 : vdim <= 1024 ? 256 : 1024);
+    if (f32)
+      launch(head_norm_gate_wide_kernel<float>, gw, bw, 0, st, true, o, den, (const float*)w, w_stride, (const float*)gate, ld_gate, gate_off, (float*)out,
+             heads, vdim, eps, act);
+    else
+      launch(head_norm_gate_wide_kernel<bf16>, gw, bw, 0, st, true, o, den, (const bf16*)w, w_stride, (const bf16*)gate, ld_gate, gate_off, (bf16*)out,
+             heads, vdim, eps, act);
+    return (int)cudaGetLastError();
+  }
   const dim3 g((unsigned)((pairs + 3) / 4));
   if (f32)
     launch(head_norm_gate_kernel<float>, g, dim3(128), 0, st, true, o, den, (const float*)w, w_stride, (const float*)gate, ld_gate, gate_off, (float*)out,

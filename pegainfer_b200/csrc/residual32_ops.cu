@@ -466,6 +466,26 @@ __global__ void embed_scaled_norm_kernel(const E* __restrict__ embed, const int*
   }
 }
 
+// sums of two values over the CTA, the same on every thread: lanes by shuffles, then the warps' partial sums in warp order (a fixed
+// order, so a row's result does not depend on timing).  red: 64 floats of shared memory.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();  // the previous use of `red` has been read
+  if (lane == 0) {
+    red[w] = a;
+    red[32 + w] = b;
+  }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  for (int i = 0; i < nw; ++i) {
+    ta += red[i];
+    tb += red[32 + i];
+  }
+  return make_float2(ta, tb);
+}
+
 template <typename E, typename Y>
 __global__ void branches_add_norm_kernel(const Y* __restrict__ ya, const E* __restrict__ wa, const E* __restrict__ yb, const E* __restrict__ wb, float mult,
                                          float* __restrict__ x, const E* __restrict__ w_next, E* __restrict__ h, float* __restrict__ h32, int width,
@@ -473,35 +493,42 @@ __global__ void branches_add_norm_kernel(const Y* __restrict__ ya, const E* __re
   extern __shared__ float gn_sm[];
   float* row = gn_sm;         // branch a, then the new residual row
   float* rowb = row + width;  // branch b
-  float* inv_s = rowb + width;
-  float* part_s = inv_s + 1;
+  float* red = rowb + width;  // 64 floats
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x;
   const size_t at = (size_t)t * width;
+  for (int i = threadIdx.x * 32; i < width; i += blockDim.x * 32) {  // what the later phases read, on its way while the sums are made
+    prefetch_l2(x + at + i);
+    if (wa) prefetch_l2(wa + i);
+    if (wb) prefetch_l2(wb + i);
+    if (w_next) prefetch_l2(w_next + i);
+  }
+  float sa = 0.f, sb = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    row[i] = ya ? to_f(ya[at + i]) : 0.f;
-    rowb[i] = yb ? to_f(yb[at + i]) : 0.f;
+    const float a = ya ? to_f(ya[at + i]) : 0.f, b = yb ? to_f(yb[at + i]) : 0.f;
+    row[i] = a;
+    rowb[i] = b;
+    sa = fmaf(a, a, sa);
+    sb = fmaf(b, b, sb);
   }
   float inv_a = 1.f, inv_b = 1.f;
-  if (ya && wa) {
-    group_inv_rms(row, width, 1, eps, part_s, inv_s);
-    inv_a = inv_s[0];
+  if ((ya && wa) || (yb && wb)) {  // both branches' sums of squares in one pass
+    const float2 ss = block_sum2(sa, sb, red);
+    inv_a = 1.f / sqrtf(ss.x / (float)width + eps);
+    inv_b = 1.f / sqrtf(ss.y / (float)width + eps);
   }
-  if (yb && wb) {
-    group_inv_rms(rowb, width, 1, eps, part_s, inv_s);
-    inv_b = inv_s[0];
-  }
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  float sr = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {  // every thread meets the entries it wrote itself
     const float a = ya ? (wa ? row[i] * inv_a * to_f(wa[i]) : row[i]) : 0.f;
     const float b = yb ? (wb ? rowb[i] * inv_b * to_f(wb[i]) : rowb[i]) : 0.f;
     const float r = x[at + i] + mult * (a + b);
     x[at + i] = r;
     row[i] = r;
+    sr = fmaf(r, r, sr);
   }
   if (!w_next) return;
-  group_inv_rms(row, width, 1, eps, part_s, inv_s);
-  const float inv = inv_s[0];
+  const float inv = 1.f / sqrtf(block_sum2(sr, 0.f, red).x / (float)width + eps);
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float v = row[i] * inv * to_f(w_next[i]);
     h[at + i] = from_f<E>(v);
@@ -741,7 +768,7 @@ extern "C" int pk_res32_embed_scaled_norm(const void* embed, const int* token_id
 extern "C" int pk_res32_branches_add_norm(const void* ya, int ya_is_f32, const void* wa, const void* yb, const void* wb, float mult, float* x,
                                           const void* w_next, void* h, float* h32, int width, float eps, int tokens, int f32, pk_stream st) {
   if (!x || (w_next && !h) || width <= 0 || tokens <= 0) return -1;
-  const size_t sm = gnorm_smem(2 * width, 1);
+  const size_t sm = (size_t)(2 * width + 64) * sizeof(float);
   const dim3 g(tokens), b(gnorm_threads(width, tokens));
   if (f32) {
     if (!gnorm_fits(branches_add_norm_kernel<float, float>, sm)) return -2;

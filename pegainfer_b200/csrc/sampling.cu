@@ -158,7 +158,29 @@ __global__ void top1_rows_f32_kernel(const float* __restrict__ logits, int* __re
   const float* x = logits + (size_t)blockIdx.x * vocab;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  int i0 = 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {  // 16-byte loads, four of them in flight per thread
+    const int n4 = vocab >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int i = threadIdx.x; i < n4; i += 4 * blockDim.x) {
+      float4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = i + u * blockDim.x < n4 ? x4[i + u * blockDim.x] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int at = (i + u * blockDim.x) * 4;
+        const float e[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (e[k] > bv || (e[k] == bv && at + k < bi)) {
+            bv = e[k];
+            bi = at + k;
+          }
+      }
+    }
+    i0 = n4 << 2;
+  }
+  for (int i = i0 + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = x[i];
     if (v > bv || (v == bv && i < bi)) {
       bv = v;

@@ -250,6 +250,21 @@ def test_scaled_embedding_with_first_norm_and_capped_logits(lib, dtype):
     assert torch.allclose(out0.cpu(), z.float() * 0.7, atol=1e-6)
 
 
+@pytest.mark.parametrize("vocab", [37, 4096, 32771])
+def test_greedy_token_of_fp32_rows(lib, vocab):
+    """highest value, lowest index on ties; rows that start on and off a 16-byte boundary"""
+    g = torch.Generator().manual_seed(13)
+    z = torch.randn(4, vocab, generator=g)
+    z[1, [5, vocab - 1]] = 9.0
+    z[2, [vocab - 2, vocab - 3]] = 9.0
+    z[3, vocab - 1] = 9.0
+    out = torch.zeros(4, dtype=torch.int32, device="cuda")
+    zd = z.cuda()
+    assert lib.pk_top1_rows_f32(zd.data_ptr(), out.data_ptr(), 4, vocab, None) == 0
+    torch.cuda.synchronize()
+    assert out.tolist() == [int(z[0].argmax()), 5, vocab - 3, vocab - 1]
+
+
 def paged(req_lens, page_size, shuffle_seed=0):
     """A page table with pages handed out in a scrambled order: (pages flat, page_off per request, number of pages)."""
     need = [(n + page_size - 1) // page_size for n in req_lens]
@@ -519,9 +534,11 @@ def test_state_space_recurrence_in_portions_over_reused_slots(lib, dtype, H, G, 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("groups", [1, 3, 6])
-def test_gate_before_the_grouped_norm(lib, dtype, groups):
+@pytest.mark.parametrize("inner", [6 * 14, 6 * 256])
+def test_gate_before_the_grouped_norm(lib, dtype, groups, inner):
+    """groups of 256 entries and more take the kernel with one CTA per (token, group)"""
     P = Hold()
-    T, inner, ld, off, eps = 5, 6 * 14, 6 * 14 + 9, 4, 1e-5
+    T, ld, off, eps = 5, inner + 9, 4, 1e-5
     g = torch.Generator().manual_seed(10)
     y, z = 3 * torch.randn(T, inner, generator=g), torch.zeros(T, ld)
     z[:, off:off + inner] = torch.randn(T, inner, generator=g)
@@ -534,7 +551,7 @@ def test_gate_before_the_grouped_norm(lib, dtype, groups):
     zz = z[:, off:off + inner]
     gated = y * (zz * torch.sigmoid(zz))
     want = O.rms(gated.reshape(T, groups, -1), eps).reshape(T, inner) * wn
-    assert torch.allclose(out.float().cpu(), want, atol=1e-5 if dtype == F32 else 3e-2)
+    assert torch.allclose(out.float().cpu(), want, atol=1e-5 if dtype == F32 else 3e-2, rtol=1e-5 if dtype == F32 else 2e-2)
 
 
 def test_router_takes_the_largest_logits_and_weighs_them_alone(lib):
