@@ -103,7 +103,18 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
     for (int e = threadIdx.x * 64; e < (norm_kind == 1 ? dim : nq + nk); e += blockDim.x * 64)
       prefetch_l2(norm_kind == 1 ? (e < dim ? qw + e : kw + e - dim) : (e < nq ? qw + e : kw + e - nq));  // a line of 64 entries each
   if (norm_kind == 1 && threadIdx.x * 64 < dim) prefetch_l2(kw + threadIdx.x * 64);
-  for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) row[e] = to_f(src[e]);
+  // 16-byte accesses where every piece of the row and of the slot starts on such a boundary (bf16, sizes multiples of 8)
+  const bool vec = sizeof(E) == 2 && ((nq | nk | nv | ld | (int)(page_stride & 7)) & 7) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(cache)) & 15) == 0;
+  if (vec) {
+    for (int e = threadIdx.x * 8; e < nq + nk; e += blockDim.x * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + e);
+      *reinterpret_cast<float4*>(row + e) = make_float4(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y));
+      *reinterpret_cast<float4*>(row + e + 4) = make_float4(bf16_lo(u.z), bf16_hi(u.z), bf16_lo(u.w), bf16_hi(u.w));
+    }
+  } else {
+    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) row[e] = to_f(src[e]);
+  }
   __syncthreads();
   if (norm_kind) {
     for (int hd = warp; hd < H + G; hd += nw) {
@@ -156,10 +167,12 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
     if (e < nq) q_out[(size_t)t * nq + e] = from_f<E>(v * stretch);
     else slot[e - nq] = from_f<E>(v);
   }
-  if (v_from_k) {
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) slot[nk + e] = src[nq + e];
+  const E* vsrc = src + (v_from_k ? nq : nq + nk);  // the values: the keys as projected, or the value projection
+  const int n_val = v_from_k ? nk : nv;
+  if (vec) {
+    for (int e = threadIdx.x * 8; e < n_val; e += blockDim.x * 8) *reinterpret_cast<uint4*>(slot + nk + e) = *reinterpret_cast<const uint4*>(vsrc + e);
   } else {
-    for (int e = threadIdx.x; e < nv; e += blockDim.x) slot[nk + e] = src[nq + nk + e];
+    for (int e = threadIdx.x; e < n_val; e += blockDim.x) slot[nk + e] = vsrc[e];
   }
 }
 
