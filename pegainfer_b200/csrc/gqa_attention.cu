@@ -134,38 +134,37 @@ __global__ void gqa_norm_append_kernel(const E* __restrict__ qkv, int ld, const 
     iq = 1.f / sqrtf(sq / (float)nq + eps);
     ik = 1.f / sqrtf(sk / (float)nk + eps);
   }
-  // normed entry e of the row [q | k]
-  auto normed = [&](int e) {
-    if (!norm_kind) return row[e];
-    const bool is_q = e < nq;
-    const int el = is_q ? e : e - nq;
-    if (norm_kind == 1) return row[e] * (1.f / sqrtf(inv[e / dim] / (float)dim + eps)) * to_f((is_q ? qw : kw)[el % dim]);
-    return row[e] * (is_q ? iq : ik) * to_f((is_q ? qw : kw)[el]);
-  };
   const float stretch = temp_every > 0 ? 1.f + temp_coef * logf((float)((p + 1) / temp_every) + 1.f) : 1.f;
   E* slot = cache + (size_t)page * page_stride + (size_t)(p % page_size) * (nk + nv);
-  for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
-    float v = normed(e);
-    const int d = e % dim;
-    if (d < dims) {
-      int i, pe;
-      bool first;
-      if (interleaved) {
-        i = d >> 1;
-        first = (d & 1) == 0;
-        pe = first ? e + 1 : e - 1;
-      } else {
-        first = d < half;
-        i = first ? d : d - half;
-        pe = first ? e + half : e - half;
+  // norm, rotation and the query's factor head by head (a warp per head, lanes over its entries: no index arithmetic per entry)
+  for (int hd = warp; hd < H + G; hd += nw) {
+    const bool is_q = hd < H;
+    const float f = norm_kind == 1 ? 1.f / sqrtf(inv[hd] / (float)dim + eps) : norm_kind == 2 ? (is_q ? iq : ik) : 1.f;
+    const E* w = norm_kind == 1 ? (is_q ? qw : kw) : norm_kind == 2 ? (is_q ? qw + hd * dim : kw + (hd - H) * dim) : nullptr;
+    const float* hrow = row + hd * dim;
+    E* dst = is_q ? q_out + (size_t)t * nq + hd * dim : slot + (hd - H) * dim;
+    const float out_f = is_q ? stretch : 1.f;
+    for (int d = lane; d < dim; d += 32) {
+      float v = hrow[d] * f * (w ? to_f(w[d]) : 1.f);
+      if (d < dims) {
+        int i, pd;
+        bool first;
+        if (interleaved) {
+          i = d >> 1;
+          first = (d & 1) == 0;
+          pd = first ? d + 1 : d - 1;
+        } else {
+          first = d < half;
+          i = first ? d : d - half;
+          pd = first ? d + half : d - half;
+        }
+        const float o = hrow[pd] * f * (w ? to_f(w[pd]) : 1.f);
+        const float a = (float)p * freq[i];
+        const float c = cosf(a) * mag, sn = sinf(a) * mag;
+        v = first ? v * c - o * sn : v * c + o * sn;
       }
-      const float a = (float)p * freq[i];
-      const float c = cosf(a) * mag, sn = sinf(a) * mag;
-      const float o = normed(pe);
-      v = first ? v * c - o * sn : v * c + o * sn;
+      dst[d] = from_f<E>(v * out_f);
     }
-    if (e < nq) q_out[(size_t)t * nq + e] = from_f<E>(v * stretch);
-    else slot[e - nq] = from_f<E>(v);
   }
   const E* vsrc = src + (v_from_k ? nq : nq + nk);  // the values: the keys as projected, or the value projection
   const int n_val = v_from_k ? nk : nv;
