@@ -816,12 +816,12 @@ def _goguzen_sizes():
         moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": sff, "limit": 7.0}}
         att = {"type": "attention", "mlp": moe,
                "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window, "keep_first": 64}, "scale": dim ** -0.5,
-                         "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}}
+                         "rot": {"dims": dim // 2, "base": 1000000.0, "scaling": {"factor": 16.0, "low": 1.0, "high": 8.0, "original": 4096}}}}
         par = {"type": "parallel", "mlp": moe,
                "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}},
                          "right": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 8}}}
         return {"architecture": "Goguzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
-                "logit_softcap": 30.0, "layers": [par, att, dict(par, weights_of=0), att]}
+                "logit_softcap": 50.0, "layers": [par, att, dict(par, weights_of=0), att]}
     return {"w2048": gog(2048, 16, 4, 128, 1024, 64, 6, 1408, 2816, 32768), "w1024": gog(1024, 8, 2, 64, 1024, 16, 2, 768, 1536, 32768)}
 
 

@@ -723,7 +723,7 @@ def random_cfg(seed):
     own_at = [i for i, l in enumerate(layers) if l != -1]
     layers = [l if l != -1 else own_at[r.randrange(n_own)] for l in layers]
     return model_cfg(layers, vocab=r.randint(40, 300), width=r.choice([24, 36, 40, 64, 100]), eps=r.choice([1e-5, 1e-6]), embed=r.uniform(0.5, 4.0),
-                     logit=r.uniform(0.2, 2.0), cap=r.choice([0.0, 5.0, 30.0]))
+                     logit=r.uniform(0.2, 2.0), cap=r.choice([0.0, 5.0, 25.0]))
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
