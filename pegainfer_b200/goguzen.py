@@ -29,7 +29,7 @@ All sizes and constants come from the configuration; nothing here depends on one
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 
 import torch
 
@@ -167,17 +167,22 @@ class GoguzenConfig:
 
     @staticmethod
     def from_dict(raw: dict, name: str = "custom") -> "GoguzenConfig":
-        layers = tuple(GoguzenLayerConfig.parse(l) for l in raw["layers"])
+        layers = [GoguzenLayerConfig.parse(l) for l in raw["layers"]]
         for i, l in enumerate(layers):
             if l.weights_of is None:
                 continue
-            if not 0 <= l.weights_of < len(layers) or layers[l.weights_of].weights_of is not None:
-                raise ValueError(f"layer {i}: weights_of must name a layer with weights of its own")
+            j, hops = l.weights_of, 0
+            while 0 <= j < len(layers) and layers[j].weights_of is not None and hops <= len(layers):
+                j, hops = layers[j].weights_of, hops + 1  # a borrower of a borrower runs with the weights at the end of the chain
+            if not 0 <= j < len(layers) or layers[j].weights_of is not None:
+                raise ValueError(f"layer {i}: weights_of must lead to a layer with weights of its own")
+            if j != l.weights_of:
+                layers[i] = l = replace(l, weights_of=j)
             o = layers[l.weights_of]
             if (l.kind, l.attention, l.state_space, l.mlp) != (o.kind, o.attention, o.state_space, o.mlp):
                 raise ValueError(f"layer {i}: its entry differs from layer {l.weights_of}, whose weights it uses")
         return GoguzenConfig(int(raw["vocab"]), int(raw["width"]), float(raw["norm"]["eps"]), float((raw.get("embedding") or {}).get("scale", 1.0)),
-                             float(raw.get("logit_scale", 1.0)), float(raw.get("logit_softcap") or 0.0), layers, name)
+                             float(raw.get("logit_scale", 1.0)), float(raw.get("logit_softcap") or 0.0), tuple(layers), name)
 
     def to_dict(self) -> dict:
         """The ``config.json`` form (round-trips through ``from_dict``)."""

@@ -47,6 +47,16 @@ def test_a_borrowing_layer_must_equal_its_owner():
         GoguzenConfig.from_dict(bad)
 
 
+def test_a_chain_of_borrowers_ends_at_the_owner():
+    chain = json.loads(json.dumps(CFG))
+    chain["layers"].append(dict(chain["layers"][2], weights_of=2))
+    c = GoguzenConfig.from_dict(chain)
+    assert [l.weights_of for l in c.layers] == [None, None, 0, 0]
+    chain["layers"][0]["weights_of"] = 3  # a ring has no owner
+    with pytest.raises(ValueError):
+        GoguzenConfig.from_dict(chain)
+
+
 def test_layer_struct_carries_the_designs_constants():
     from pegainfer_b200.goguzen import GoguzenModel
     from pegainfer_b200.layered import ModelCfg
